@@ -1,0 +1,412 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Headline metric: W4 g128 decode qmatmul throughput in GB/s of ALGORITHMIC bytes
+(packed weights + fp16 scale/zero-point + activations in + outputs out, per launch).
+
+Workloads
+  decode8b   (default at N=1) one step = one decode pass of M in {1,2,4,8,16} tokens over a
+             stack of Llama-3-8B-shaped W4 g128 linears (4096->4096, 4096->1024, 4096->14336,
+             14336->4096), `--layers` distinct copies of each so that every launch reads weights
+             that are not in L2 (the stack is several times the 126 MB L2).
+  tp70b      (default at N>1) one step = decode batch 64 through the seven W4 g128 linears of
+             Llama-3-70B-shaped decoder layers, tensor-parallel over N GPUs (column-parallel
+             q/k/v/gate/up, row-parallel o/down + NCCL all-reduce), strong scaling.
+Synthetic data: weights ~ N(0, 0.02) rounded to bf16 and RTN-quantized on the device by this
+library's own kernel; activations ~ N(0, 1) bf16.  No checkpoint or dataset is involved.
+
+The line printed by rank 0 carries `value` (inputs resident in HBM), `e2e` (the same work
+through the host-buffer call: pinned host activations in, host outputs back, copies inside the
+timed region), `roofline` for the decode kernel against the measured HBM peak, and
+`cpu_baseline` (the CPU oracle on the host cores over a bounded sample).  `--impl reference`
+times the CPU implementation of the same path instead (the oracle port of the reference's
+CPU code; the reference's own forward cannot run without a GPU).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA8B_SHAPES = [("q_o_proj", 4096, 4096), ("kv_proj", 1024, 4096), ("gate_up_proj", 14336, 4096),
+                  ("down_proj", 4096, 14336)]
+DECODE_M = [1, 2, 4, 8, 16]
+FALLBACK_HBM_GBS = 6650.0
+
+
+def decode_bytes(M, N, K, bits, g, bias=False):
+    """Algorithmic bytes of one decode qmatmul launch."""
+    return N * K * bits // 8 + 2 * N * (K // g) * 2 + 2 * M * K + 2 * M * N + (2 * N if bias else 0)
+
+
+def rtn_bytes(N, K, bits, g, s_in):
+    return N * K * s_in + N * K * bits // 8 + N * (K // g) * 8
+
+
+def read_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d.get("bf16_tflops", 0)),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", 0)), "source": "measured"}
+    return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's CPU code, all host threads
+# ------------------------------------------------------------------------------------------
+
+def cpu_decode_sample(sample_shapes, Ms, bits=4, g=128, repeats=1):
+    """Times the CPU oracle (quantized forward = dequantize + matmul, restating the reference's
+    bitween/functional.py:47-71 + bitween/modules.py:97-101) on a bounded sample."""
+    import numpy as np
+    from bitween_b200 import synth
+    from oracle import oracle
+    total_bytes, total_s = 0, 0.0
+    for (name, N, K) in sample_shapes:
+        w = synth.normal(11, (N, K), 0.02)
+        q, s, z = oracle.quantize_rtn(w, oracle.F32, bits, g)
+        s_h = oracle.f16_bits(s)
+        z_h = oracle.f16_bits(z.astype(np.float32))
+        for M in Ms:
+            x = oracle.f16_bits(synth.normal(12 + M, (M, K), 1.0))
+            for _ in range(repeats):
+                t0 = time.perf_counter()
+                oracle.qlinear_forward(x, q, s_h, z_h, None, bits, g)
+                total_s += time.perf_counter() - t0
+                total_bytes += decode_bytes(M, N, K, bits, g)
+    return total_bytes, total_s
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    from oracle import oracle
+    oracle.build()
+    sample = [LLAMA8B_SHAPES[1], LLAMA8B_SHAPES[0]]      # 4096->1024 and 4096->4096
+    Ms = DECODE_M
+    for _ in range(args.warmup):
+        cpu_decode_sample(sample[:1], [1])
+    t_all, b_all = 0.0, 0
+    for _ in range(args.steps):
+        b, s = cpu_decode_sample(sample, Ms)
+        t_all += s
+        b_all += b
+    val = b_all / t_all / 1e9
+    cores = oracle.num_threads()
+    desc = "M in {1,2,4,8,16} x {4096->1024, 4096->4096} W4 g128 per step (bounded sample of the decode sweep)"
+    line = {"impl": "reference", "metric": "w4g128_qmatmul_decode_GBps", "value": val, "unit": "GB/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": t_all / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "decode8b", "sample": desc},
+            "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port", "sample": desc},
+            "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+
+class Layer:
+    """One RTN-quantized linear resident on the device (packed codes + fp16 scale/zero-point)."""
+
+    def __init__(self, N, K, bits, g, device, gen, torch, fn):
+        w = (torch.randn(N, K, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+        self.q, self.scale, self.zp = fn.quantize_rtn_to_module_buffers(w, bits, g)
+        self.N, self.K, self.bits, self.g = N, K, bits, g
+
+
+def time_region(torch, fn, stream=None):
+    """CUDA-event duration (ms) of fn() on the current stream, synchronised on both sides."""
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1)
+
+
+def run_decode8b(args, torch, dist, rank, world, device):
+    from bitween_b200 import functional as fn
+    from bitween_b200.kernels import _lib
+    from bitween_b200.kernels.cuda_loader import quantized_matmul_cuda, quantized_matmul_host
+    bits, g = 4, 128
+    gen = torch.Generator(device=device).manual_seed(1234 + rank)
+    layers = [[Layer(N, K, bits, g, device, gen, torch, fn) for (_, N, K) in LLAMA8B_SHAPES]
+              for _ in range(args.layers)]
+    xs = {M: {K: torch.randn(M, K, device=device, generator=gen).to(torch.bfloat16) for K in (4096, 14336)}
+          for M in DECODE_M}
+    outs = {M: {N: torch.empty(M, N, device=device, dtype=torch.float16) for N in (4096, 1024, 14336)}
+            for M in DECODE_M}
+
+    def step():
+        for M in DECODE_M:
+            for stack in layers:
+                for L in stack:
+                    quantized_matmul_cuda(xs[M][L.K], L.q, L.scale, L.zp, None, bits, g, out=outs[M][L.N])
+
+    launches_per_step = len(DECODE_M) * args.layers * len(LLAMA8B_SHAPES)
+    bytes_per_step = sum(decode_bytes(M, N, K, bits, g) for M in DECODE_M for (_, N, K) in LLAMA8B_SHAPES) * args.layers
+
+    for _ in range(max(args.warmup, 1) if not args.graph else 1):
+        step()
+    graph = None
+    if args.graph:
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        run_step = graph.replay
+    else:
+        run_step = step
+    for _ in range(args.warmup):
+        run_step()
+
+    sampler = ClockSampler(device.index)
+    if dist is not None:
+        dist.barrier()
+    sampler.start()
+    ms = time_region(torch, lambda: [run_step() for _ in range(args.steps)])
+    clocks = sampler.stop()
+    if dist is not None:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = bytes_per_step * args.steps * world / (ms * 1e-3) / 1e9
+
+    # ---- end to end: pinned host activations in, host outputs back, per launch ----------
+    hx = {M: {K: torch.randn(M, K).to(torch.bfloat16).pin_memory() for K in (4096, 14336)} for M in DECODE_M}
+    hy = {M: {N: torch.empty(M, N, dtype=torch.float16).pin_memory() for N in (4096, 1024, 14336)} for M in DECODE_M}
+
+    def e2e_step():
+        for M in DECODE_M:
+            for stack in layers:
+                for L in stack:
+                    quantized_matmul_host(hx[M][L.K], L.q, L.scale, L.zp, None, bits, g, hy[M][L.N],
+                                          xs[M][L.K], outs[M][L.N])
+    h2d = sum(2 * M * K for M in DECODE_M for (_, N, K) in LLAMA8B_SHAPES) * args.layers
+    d2h = sum(2 * M * N for M in DECODE_M for (_, N, K) in LLAMA8B_SHAPES) * args.layers
+    for _ in range(2):
+        e2e_step()
+    e2e_steps = max(1, min(args.steps, 5))
+    ms_e2e = time_region(torch, lambda: [e2e_step() for _ in range(e2e_steps)])
+    if dist is not None:
+        t = torch.tensor([ms_e2e], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = float(t.item())
+    e2e_val = bytes_per_step * e2e_steps * world / (ms_e2e * 1e-3) / 1e9
+
+    # ---- per-shape breakdown (M = 1 and 16), each launch on weights that are not in L2 ----
+    breakdown = {}
+    if rank == 0:
+        for si, (name, N, K) in enumerate(LLAMA8B_SHAPES):
+            for M in (1, 16):
+                def one():
+                    for stack in layers:
+                        L = stack[si]
+                        quantized_matmul_cuda(xs[M][K], L.q, L.scale, L.zp, None, bits, g, out=outs[M][N])
+                for _ in range(3):
+                    one()
+                reps = 5
+                t_ms = time_region(torch, lambda: [one() for _ in range(reps)]) / (reps * args.layers)
+                breakdown[f"{name}_{N}x{K}_M{M}"] = {
+                    "us": round(t_ms * 1e3, 2),
+                    "GBps": round(decode_bytes(M, N, K, bits, g) / (t_ms * 1e-3) / 1e9, 1)}
+
+    extra = {}
+    if rank == 0 and not args.no_extra:
+        extra = run_extras(args, torch, fn, quantized_matmul_cuda, device, gen)
+
+    return {"value": value, "ms": ms, "launches": launches_per_step * args.steps, "clocks": clocks,
+            "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps},
+            "bytes_per_launch": bytes_per_step / launches_per_step, "launches_per_step": launches_per_step,
+            "breakdown": breakdown, "extra": extra, "kernel": _lib.last_qmatmul_kernel(),
+            "config": {"workload": "decode8b", "shapes": "Llama-3-8B linears x M{1,2,4,8,16}",
+                       "bits": bits, "group_size": g, "layer_copies": args.layers,
+                       "l2_policy": f"inputs larger than L2: {args.layers} distinct copies of every layer "
+                                    f"({args.layers * 69} MB of packed weights per pass)",
+                       "cuda_graph": bool(args.graph)}}
+
+
+def run_extras(args, torch, fn, qmm, device, gen):
+    """RTN quantize+pack GB/s and prefill TFLOP/s on the same shapes (reported, not the headline)."""
+    out = {}
+    # RTN: bf16 weights, fp32 arithmetic, fp32 scale + int32 zero-point out
+    tot_b, tot_ms = 0, 0.0
+    per = {}
+    for (name, N, K) in LLAMA8B_SHAPES:
+        ws = [(torch.randn(N, K, device=device, generator=gen) * 0.02).to(torch.bfloat16) for _ in range(3)]
+        for bits, g in ((4, 128),):
+            for w in ws[:2]:
+                fn._rtn_launch(w, bits, g, torch.float32, torch.int32, True)
+            ms = time_region(torch, lambda: [fn._rtn_launch(w, bits, g, torch.float32, torch.int32, True) for w in ws]) / len(ws)
+            b = rtn_bytes(N, K, bits, g, 2)
+            per[f"{name}_{N}x{K}"] = round(b / (ms * 1e-3) / 1e9, 1)
+            tot_b += b
+            tot_ms += ms
+        del ws
+    out["rtn_w4g128_bf16in_GBps"] = round(tot_b / (tot_ms * 1e-3) / 1e9, 1)
+    out["rtn_per_shape_GBps"] = per
+    # prefill
+    pf = {}
+    for (name, N, K) in LLAMA8B_SHAPES:
+        L = Layer(N, K, 4, 128, device, gen, torch, fn)
+        for M in (args.prefill_m,):
+            x = torch.randn(M, K, device=device, generator=gen).to(torch.float16)
+            y = torch.empty(M, N, device=device, dtype=torch.float16)
+            qmm(x, L.q, L.scale, L.zp, None, 4, 128, out=y)
+            ms = time_region(torch, lambda: [qmm(x, L.q, L.scale, L.zp, None, 4, 128, out=y) for _ in range(3)]) / 3
+            pf[f"{name}_{N}x{K}_M{M}"] = round(2.0 * M * N * K / (ms * 1e-3) / 1e12, 1)
+        del L
+    out["prefill_w4g128_TFLOPs"] = pf
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="auto")
+    ap.add_argument("--layers", type=int, default=8, help="distinct copies of each layer shape (L2 defeat)")
+    ap.add_argument("--graph", type=int, default=1, help="replay each step as one CUDA graph")
+    ap.add_argument("--prefill-m", type=int, default=2048)
+    ap.add_argument("--no-extra", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this benchmark has no CPU mode (use --impl reference)")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=device)
+        dist = dist_mod
+
+    workload = args.workload
+    if workload == "auto":
+        workload = "decode8b" if world == 1 else "tp70b"
+    if workload == "decode8b":
+        res = run_decode8b(args, torch, dist, rank, world, device)
+        scaling = "weak"
+    elif workload == "tp70b":
+        from bitween_b200 import tp_bench
+        res = tp_bench.run_tp70b(args, torch, dist, rank, world, device, ClockSampler, time_region, decode_bytes)
+        scaling = "strong"
+    else:
+        raise SystemExit(f"unknown workload {workload}")
+
+    if rank == 0:
+        peaks = read_peaks()
+        ms_per_launch = res["ms"] / max(res["launches"], 1)
+        achieved = res["bytes_per_launch"] / (ms_per_launch * 1e-3) / 1e9
+        line = {"metric": "w4g128_qmatmul_decode_GBps", "value": res["value"], "unit": "GB/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": res["ms"] / args.steps, "higher_is_better": True, "scaling": scaling,
+                "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": res["config"],
+                "clocks": res["clocks"], "e2e": res["e2e"], "gpu_launches": res["launches"],
+                "roofline": {"bound": "hbm", "kernel": res["kernel"], "achieved": achieved,
+                             "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                             "peak_source": peaks["source"], "traffic": res.get("traffic"),
+                             "us_per_launch": ms_per_launch * 1e3,
+                             "algorithmic_bytes_per_launch": res["bytes_per_launch"]},
+                "breakdown": res.get("breakdown", {}), "extra": res.get("extra", {})}
+        if world == 1 and not args.no_cpu:
+            sample = [LLAMA8B_SHAPES[1], LLAMA8B_SHAPES[0]]
+            from oracle import oracle
+            oracle.build()
+            cpu_decode_sample(sample[:1], [1])
+            b, s = cpu_decode_sample(sample, DECODE_M, repeats=2)
+            line["cpu_baseline"] = {
+                "value": b / s / 1e9, "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
+                "sample": "M in {1,2,4,8,16} x {4096->1024, 4096->4096} W4 g128, 2 repeats "
+                          f"({s:.1f} s of CPU time), oracle port of the reference's CPU dequantize+matmul"}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,178 @@
+// extern "C" entry points of libbitween_b200.so (declared in include/bitween_b200.h):
+// argument validation, status codes and kernel dispatch.  No torch types, no allocation.
+#include <cstdio>
+#include <cstring>
+
+#include "bw_common.cuh"
+
+namespace bw {
+
+static thread_local char g_cuda_error[256] = "";
+static thread_local const char *g_last_kernel = "";
+
+int record_cuda_error(cudaError_t e, const char *where) {
+    snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s (%s)", where, cudaGetErrorName(e),
+             cudaGetErrorString(e));
+    (void)cudaGetLastError();  // clear the sticky-free error state for the next call
+    return BW_ERR_CUDA;
+}
+void set_last_kernel(const char *name) { g_last_kernel = name; }
+
+// implemented in the kernel translation units
+int rtn_quantize_pack(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int g, int32_t *q,
+                      void *scale, int scale_dtype, void *zp, int zp_dtype, unsigned flags,
+                      cudaStream_t st);
+int dequantize(const int32_t *q, const void *scale, int scale_dtype, const void *zp, int zp_dtype,
+               int64_t N, int64_t K, int bits, int g, void *out, int out_dtype, cudaStream_t st);
+int qmatmul_smallm(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
+                   const __half *scale, const __half *zp, const __half *bias, void *out, int out_dtype,
+                   int bits, int g, cudaStream_t st);
+bool smallm_fast_path_ok(const void *x, int x_dtype, int64_t K, const int32_t *q, int bits, int g);
+void set_smallm_tuning(int rt, int warps, int splits);
+int qmatmul_grad_input(const void *go, int dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
+                       const __half *scale, const __half *zp, void *gi, int bits, int g, cudaStream_t st);
+
+static bool is_float_dtype(int dt) { return dt == BW_F32 || dt == BW_F16 || dt == BW_BF16; }
+
+}  // namespace bw
+
+using namespace bw;
+
+extern "C" {
+
+int bw_rtn_quantize_pack(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int group_size,
+                         int32_t *qweight, void *scale, int scale_dtype, void *zero_point,
+                         int zp_dtype, unsigned flags, void *stream) {
+    int rc = check_quant_shape(N, K, bits, group_size);
+    if (rc != BW_OK) return rc;
+    if (!is_float_dtype(w_dtype) || !is_float_dtype(scale_dtype)) return BW_ERR_DTYPE;
+    if (zp_dtype != BW_I32 && zp_dtype != BW_F16) return BW_ERR_DTYPE;
+    if (N * K == 0) return BW_OK;
+    if (!w || !qweight || !scale || !zero_point) return BW_ERR_NULL;
+    if (!aligned_to(w, dtype_size(w_dtype)) || !aligned_to(qweight, 4) ||
+        !aligned_to(scale, dtype_size(scale_dtype)) || !aligned_to(zero_point, dtype_size(zp_dtype)))
+        return BW_ERR_ALIGN;
+    return rtn_quantize_pack(w, w_dtype, N, K, bits, group_size, qweight, scale, scale_dtype,
+                             zero_point, zp_dtype, flags, (cudaStream_t)stream);
+}
+
+int bw_dequantize(const int32_t *qweight, const void *scale, int scale_dtype, const void *zero_point,
+                  int zp_dtype, int64_t N, int64_t K, int bits, int group_size, void *out,
+                  int out_dtype, void *stream) {
+    int rc = check_quant_shape(N, K, bits, group_size);
+    if (rc != BW_OK) return rc;
+    if (!is_float_dtype(scale_dtype) || !is_float_dtype(out_dtype)) return BW_ERR_DTYPE;
+    if (!is_float_dtype(zp_dtype) && zp_dtype != BW_I32) return BW_ERR_DTYPE;
+    if (N * K == 0) return BW_OK;
+    if (!qweight || !scale || !zero_point || !out) return BW_ERR_NULL;
+    if (!aligned_to(qweight, 4) || !aligned_to(scale, dtype_size(scale_dtype)) ||
+        !aligned_to(zero_point, dtype_size(zp_dtype)) || !aligned_to(out, dtype_size(out_dtype)))
+        return BW_ERR_ALIGN;
+    return dequantize(qweight, scale, scale_dtype, zero_point, zp_dtype, N, K, bits, group_size, out,
+                      out_dtype, (cudaStream_t)stream);
+}
+
+size_t bw_qmatmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int bits, int group_size) {
+    (void)M; (void)N; (void)K; (void)bits; (void)group_size;
+    return 0;  // split-K sums travel through distributed shared memory; no global scratch
+}
+
+int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *qweight,
+               const void *scale, const void *zero_point, const void *bias, void *out, int out_dtype,
+               int bits, int group_size, void *workspace, size_t workspace_bytes, void *stream) {
+    int rc = check_quant_shape(N, K, bits, group_size);
+    if (rc != BW_OK) return rc;
+    if (M < 0) return BW_ERR_SHAPE;
+    if (!is_float_dtype(x_dtype) || !is_float_dtype(out_dtype)) return BW_ERR_DTYPE;
+    if (M == 0 || N == 0) return BW_OK;
+    if (!out) return BW_ERR_NULL;
+    if (K > 0 && (!x || !qweight || !scale || !zero_point)) return BW_ERR_NULL;
+    if (!aligned_to(x, dtype_size(x_dtype)) || !aligned_to(out, dtype_size(out_dtype)) ||
+        !aligned_to(qweight, 4) || !aligned_to(scale, 2) || !aligned_to(zero_point, 2) ||
+        !aligned_to(bias, 2))
+        return BW_ERR_ALIGN;
+    if (workspace_bytes < bw_qmatmul_workspace_bytes(M, N, K, bits, group_size)) return BW_ERR_WORKSPACE;
+    (void)workspace;
+    cudaStream_t st = (cudaStream_t)stream;
+    const __half *s = (const __half *)scale, *z = (const __half *)zero_point, *b = (const __half *)bias;
+    if (K == 0) {
+        // empty reduction: out = bias (or 0); run the general kernel, which handles it
+        return qmatmul_smallm(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, st);
+    }
+    if (!smallm_fast_path_ok(x, x_dtype, K, qweight, bits, group_size))
+        return qmatmul_smallm(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, st);
+    // token blocks of at most 64 through the streaming kernel
+    const size_t xs = dtype_size(x_dtype), os = dtype_size(out_dtype);
+    for (int64_t m0 = 0; m0 < M; m0 += 64) {
+        const int64_t mc = (M - m0 < 64) ? (M - m0) : 64;
+        rc = qmatmul_smallm((const char *)x + (size_t)m0 * K * xs, x_dtype, mc, N, K, qweight, s, z, b,
+                            (char *)out + (size_t)m0 * N * os, out_dtype, bits, group_size, st);
+        if (rc != BW_OK) return rc;
+    }
+    return BW_OK;
+}
+
+int bw_qmatmul_host(const void *x_host, int x_dtype, int64_t M, int64_t N, int64_t K,
+                    const int32_t *qweight, const void *scale, const void *zero_point,
+                    const void *bias, void *out_host, int out_dtype, int bits, int group_size,
+                    void *x_dev, void *out_dev, void *workspace, size_t workspace_bytes,
+                    void *stream) {
+    if (M < 0 || N < 0 || K < 0) return BW_ERR_SHAPE;
+    if (!is_float_dtype(x_dtype) || !is_float_dtype(out_dtype)) return BW_ERR_DTYPE;
+    if (M * N == 0) return BW_OK;
+    if (!x_dev || !out_dev || !out_host || (K > 0 && !x_host)) return BW_ERR_NULL;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (M * K > 0)
+        BW_CUDA_TRY(cudaMemcpyAsync(x_dev, x_host, (size_t)(M * K) * dtype_size(x_dtype),
+                                    cudaMemcpyHostToDevice, st));
+    int rc = bw_qmatmul(x_dev, x_dtype, M, N, K, qweight, scale, zero_point, bias, out_dev, out_dtype,
+                        bits, group_size, workspace, workspace_bytes, stream);
+    if (rc != BW_OK) return rc;
+    BW_CUDA_TRY(cudaMemcpyAsync(out_host, out_dev, (size_t)(M * N) * dtype_size(out_dtype),
+                                cudaMemcpyDeviceToHost, st));
+    return BW_OK;
+}
+
+int bw_qmatmul_grad_input(const void *grad_out, int grad_dtype, int64_t M, int64_t N, int64_t K,
+                          const int32_t *qweight, const void *scale, const void *zero_point,
+                          void *grad_in, int bits, int group_size, void *stream) {
+    int rc = check_quant_shape(N, K, bits, group_size);
+    if (rc != BW_OK) return rc;
+    if (M < 0) return BW_ERR_SHAPE;
+    if (!is_float_dtype(grad_dtype)) return BW_ERR_DTYPE;
+    if (M == 0 || K == 0) return BW_OK;
+    if (!grad_in) return BW_ERR_NULL;
+    if (N > 0 && (!grad_out || !qweight || !scale || !zero_point)) return BW_ERR_NULL;
+    if (!aligned_to(grad_out, dtype_size(grad_dtype)) || !aligned_to(grad_in, dtype_size(grad_dtype)) ||
+        !aligned_to(qweight, 4) || !aligned_to(scale, 2) || !aligned_to(zero_point, 2))
+        return BW_ERR_ALIGN;
+    return qmatmul_grad_input(grad_out, grad_dtype, M, N, K, qweight, (const __half *)scale,
+                              (const __half *)zero_point, grad_in, bits, group_size,
+                              (cudaStream_t)stream);
+}
+
+const char *bw_status_string(int status) {
+    switch (status) {
+        case BW_OK: return "ok";
+        case BW_ERR_BITS: return "Only 2, 4, or 8-bit quantization supported.";
+        case BW_ERR_GROUP: return "group_size must be >= 1 and divide in_features";
+        case BW_ERR_SHAPE: return "bad shape (negative, too large, or in_features not a multiple of 32/bits)";
+        case BW_ERR_DTYPE: return "dtype not accepted for this argument";
+        case BW_ERR_ALIGN: return "pointer not aligned for its element type";
+        case BW_ERR_NULL: return "required pointer is NULL";
+        case BW_ERR_WORKSPACE: return "workspace too small";
+        case BW_ERR_CUDA: return "CUDA runtime error (see bw_last_cuda_error)";
+        case BW_ERR_UNSUPPORTED: return "no kernel for this request";
+        case BW_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+        default: return "unknown status";
+    }
+}
+
+const char *bw_last_cuda_error(void) { return g_cuda_error; }
+int bw_version(void) { return 100; }
+const char *bw_last_qmatmul_kernel(void) { return g_last_kernel; }
+
+// Not in the public header: tuning hook used by the benchmark's sweep mode.
+BW_API void bw_debug_set_smallm_tuning(int rt, int warps, int splits) { set_smallm_tuning(rt, warps, splits); }
+
+}  // extern "C"

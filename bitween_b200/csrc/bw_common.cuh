@@ -1,0 +1,62 @@
+// Shared helpers of the sm_100a kernels behind the C ABI in include/bitween_b200.h.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "bitween_b200.h"
+
+namespace bw {
+
+// Records a failed CUDA runtime call for bw_last_cuda_error(); returns BW_ERR_CUDA.
+int record_cuda_error(cudaError_t e, const char *where);
+void set_last_kernel(const char *name);
+
+#define BW_CUDA_TRY(expr)                                              \
+    do {                                                               \
+        cudaError_t _e = (expr);                                       \
+        if (_e != cudaSuccess) return ::bw::record_cuda_error(_e, #expr); \
+    } while (0)
+
+inline int check_launch(const char *where) {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? BW_OK : record_cuda_error(e, where);
+}
+
+inline bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+inline size_t dtype_size(int dt) {
+    switch (dt) {
+        case BW_F32: case BW_I32: return 4;
+        case BW_F16: case BW_BF16: return 2;
+        default: return 0;
+    }
+}
+
+// Validates the (bits, group_size, K) triple the way the reference does
+// (bitween/functional.py:6,12-17 and the reshape at :42-43).
+inline int check_quant_shape(int64_t N, int64_t K, int bits, int group_size) {
+    if (bits != 2 && bits != 4 && bits != 8) return BW_ERR_BITS;
+    if (group_size < 1) return BW_ERR_GROUP;
+    if (N < 0 || K < 0) return BW_ERR_SHAPE;
+    if (K % group_size != 0) return BW_ERR_GROUP;
+    if (K % (32 / bits) != 0) return BW_ERR_SHAPE;
+    if (N > 0 && K > (int64_t)1 << 40) return BW_ERR_SHAPE;
+    if (N * K < 0 || (K > 0 && N > ((int64_t)1 << 62) / K)) return BW_ERR_SHAPE;
+    return BW_OK;
+}
+
+// ---- device-side element load/store in fp32 ---------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f32<int32_t>(int32_t v) { return (float)v; }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+}  // namespace bw

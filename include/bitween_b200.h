@@ -1,0 +1,157 @@
+/*
+ * bitween_b200.h -- C ABI of libbitween_b200.so, the sm_100a replacement for the
+ * reference's kernel directory (bitween/kernels/) and for the eager tensor code on its
+ * RTN quantize / QuantizedLinear forward path.
+ *
+ * Conventions for every entry point:
+ *   - plain pointers and sizes only; every pointer is DEVICE memory owned by the caller
+ *     unless the name says host; nothing the caller sees is allocated here
+ *   - asynchronous on `stream` (a cudaStream_t passed as void*; NULL = default stream),
+ *     on the CUDA device that is current in the calling thread
+ *   - returns a bw_status (0 = BW_OK); never throws, aborts or traps
+ *   - tensors are dense row-major
+ *
+ * Packed-weight wire format (identical to the reference, bitween/functional.py:31-43):
+ *   vpi = 32 / bits codes per int32 word; qweight[n][j] holds the codes of
+ *   k = j*vpi .. j*vpi+vpi-1, code i in bits [i*bits, (i+1)*bits); codes are unsigned
+ *   (0 .. 2^bits-1) inside a signed int32 container; scale[n][k / group_size],
+ *   zero_point[n][k / group_size]; dequantized weight = scale * (code - zero_point).
+ */
+#ifndef BITWEEN_B200_H_
+#define BITWEEN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define BW_API __attribute__((visibility("default")))
+#else
+#define BW_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    BW_F32 = 0,
+    BW_F16 = 1,
+    BW_BF16 = 2,
+    BW_I32 = 3
+} bw_dtype;
+
+typedef enum {
+    BW_OK = 0,
+    BW_ERR_BITS = 1,        /* bits not in {2,4,8}            (AssertionError in the reference) */
+    BW_ERR_GROUP = 2,       /* group_size < 1 or K % group_size != 0   (ValueError)            */
+    BW_ERR_SHAPE = 3,       /* negative size, K % (32/bits) != 0, size overflow                */
+    BW_ERR_DTYPE = 4,       /* dtype code not accepted by this argument                        */
+    BW_ERR_ALIGN = 5,       /* pointer not aligned for its element type                        */
+    BW_ERR_NULL = 6,        /* required pointer is NULL                                        */
+    BW_ERR_WORKSPACE = 7,   /* workspace smaller than bw_qmatmul_workspace_bytes()             */
+    BW_ERR_CUDA = 8,        /* a CUDA runtime call failed; see bw_last_cuda_error()            */
+    BW_ERR_UNSUPPORTED = 9, /* valid request this build has no kernel for                      */
+    BW_ERR_TIMEOUT = 10     /* a bounded device-side wait ran out (reported via status word)   */
+} bw_status;
+
+/* flags for bw_rtn_quantize_pack */
+#define BW_RTN_UPCAST_F32 1u /* 16-bit weights: up-cast each element to fp32 and do all
+                                arithmetic in fp32, i.e. what QuantizedLinear.from_float gets
+                                from `deepcopy(layer).to(float32)` (bitween/modules.py:191)   */
+
+/*
+ * RTN group-wise quantize + pack.  Replaces bitween/functional.py:3-45 (quantize_rtn): per
+ * group of `group_size` consecutive input-dim elements of each row, min/max, scale =
+ * max((max-min)/Qmax, 1e-8), zero_point = clamp(round(-min/scale), 0, Qmax), codes =
+ * clamp(round(w/scale + zero_point), 0, Qmax), packed into int32 words.  Every operation
+ * is rounded exactly as torch's op-by-op evaluation in the weight dtype, so the outputs
+ * are bit-identical to the reference run on CPU.
+ *
+ *   w          [N,K]            BW_F32 | BW_F16 | BW_BF16
+ *   qweight    [N,K*bits/32]    int32 out
+ *   scale      [N,K/group_size] out; BW_F32 | BW_F16 | BW_BF16.  The reference returns the
+ *                               weight dtype; BW_F16 applies the fp32->fp16 copy_ cast of
+ *                               QuantizedLinear.from_float (bitween/modules.py:208) in place.
+ *   zero_point [N,K/group_size] out; BW_I32 (reference API) or BW_F16 (module buffer,
+ *                               bitween/modules.py:209)
+ */
+BW_API int bw_rtn_quantize_pack(const void *w, int w_dtype, int64_t N, int64_t K, int bits,
+                         int group_size, int32_t *qweight, void *scale, int scale_dtype,
+                         void *zero_point, int zp_dtype, unsigned flags, void *stream);
+
+/*
+ * Dequantize packed weights: out[n][k] = out_dtype( float(scale) * (float(code) - float(zp)) ).
+ * With BW_F32 scale / BW_I32 zero_point / BW_F32 out it replaces bitween/functional.py:47-71
+ * (dequantize_rtn); with BW_F16 scale and zero_point and BW_F16 out it replaces the Triton
+ * kernel bitween/modules.py:10-58; it is also the weight reconstruction of the backward
+ * pass (bitween/modules.py:121-135).
+ *   scale: BW_F32|BW_F16|BW_BF16   zero_point: BW_I32|BW_F32|BW_F16|BW_BF16
+ *   out  : BW_F32|BW_F16|BW_BF16
+ */
+BW_API int bw_dequantize(const int32_t *qweight, const void *scale, int scale_dtype,
+                  const void *zero_point, int zp_dtype, int64_t N, int64_t K, int bits,
+                  int group_size, void *out, int out_dtype, void *stream);
+
+/*
+ * QuantizedLinear forward: out[m][n] = sum_k x[m][k] * W[n][k] (+ bias[n]),
+ * W[n][k] = fp16( scale * (code - zero_point) ).  Replaces
+ * QuantizedLinearFunction.forward, bitween/modules.py:61-106 (Triton dequantize to a
+ * temporary fp16 [N,K] + torch.matmul + bias add), and is the body of the
+ * `quantized_matmul_cuda(x, qweight, scale, zero_point, bias, bits, group_size)` symbol the
+ * reference's scripts import (main.py:401,433).
+ *
+ *   x        [M,K]  BW_F16 | BW_BF16 | BW_F32; cast to fp16 first, as bitween/modules.py:74
+ *   qweight  [N,K*bits/32] int32
+ *   scale    [N,K/group_size] fp16          (module buffer dtype, bitween/modules.py:177)
+ *   zero_point [N,K/group_size] fp16, integer-valued in [0,255]  (bitween/modules.py:178)
+ *   bias     [N] fp16 or NULL
+ *   out      [M,N]  BW_F16: fp16(fp16(acc) + bias), the reference's two roundings
+ *                   (bitween/modules.py:97,101); BW_BF16: bf16(acc + bias);
+ *                   BW_F32: acc + bias with no 16-bit rounding (fp32-accumulate checks)
+ *   workspace       device scratch of at least bw_qmatmul_workspace_bytes(...) bytes, or
+ *                   NULL when that is 0.  Calls that overlap on the GPU must not share it.
+ * Accumulation is fp32.  The kernel is chosen from M (small-M streaming kernel, large-M
+ * tensor-core GEMM); unusual group sizes run on a slower general kernel, never on the CPU.
+ */
+BW_API size_t bw_qmatmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int bits, int group_size);
+
+BW_API int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K,
+               const int32_t *qweight, const void *scale, const void *zero_point,
+               const void *bias, void *out, int out_dtype, int bits, int group_size,
+               void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Same operator with HOST activations and HOST output (pinned memory for true overlap):
+ * copies x to `x_dev`, runs bw_qmatmul, copies the result from `out_dev` to `out_host`, all
+ * asynchronously on `stream`.  The packed weights stay resident on the device.  This is the
+ * end-to-end call timed by the benchmark (host<->device copies inside the timed region).
+ */
+BW_API int bw_qmatmul_host(const void *x_host, int x_dtype, int64_t M, int64_t N, int64_t K,
+                    const int32_t *qweight, const void *scale, const void *zero_point,
+                    const void *bias, void *out_host, int out_dtype, int bits, int group_size,
+                    void *x_dev, void *out_dev, void *workspace, size_t workspace_bytes,
+                    void *stream);
+
+/*
+ * grad_input of QuantizedLinearFunction.backward (bitween/modules.py:108-141):
+ * grad_in[m][k] = sum_n grad_out[m][n] * W[n][k], W = dtype( scale * (code - zero_point) )
+ * evaluated in fp32 and cast to the gradient dtype (bitween/modules.py:131-139).
+ *   grad_out [M,N], grad_in [M,K]: BW_F16 | BW_BF16 | BW_F32 (same dtype for both)
+ */
+BW_API int bw_qmatmul_grad_input(const void *grad_out, int grad_dtype, int64_t M, int64_t N, int64_t K,
+                          const int32_t *qweight, const void *scale, const void *zero_point,
+                          void *grad_in, int bits, int group_size, void *stream);
+
+/* Human-readable text for a bw_status. */
+BW_API const char *bw_status_string(int status);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+BW_API const char *bw_last_cuda_error(void);
+/* Library version: major*10000 + minor*100 + patch. */
+BW_API int bw_version(void);
+/* Name of the kernel the last bw_qmatmul call of this thread dispatched to (diagnostics). */
+BW_API const char *bw_last_qmatmul_kernel(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BITWEEN_B200_H_ */

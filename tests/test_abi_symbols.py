@@ -1,0 +1,44 @@
+"""The C-ABI library loads and exports every symbol include/bitween_b200.h declares.
+No compute call is made here, so this runs without a GPU."""
+import ctypes
+import os
+import re
+
+from bitween_b200.kernels import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "bitween_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return re.findall(r"BW_API[^;(]*?\b(bw_[a-z_0-9]+)\s*\(", text)
+
+
+def test_every_declared_symbol_is_exported():
+    names = declared_symbols()
+    assert len(names) >= 10 and "bw_qmatmul" in names and "bw_rtn_quantize_pack" in names
+    L = _lib.lib()
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert hasattr(raw, n), f"{n} declared in the header but not exported"
+    assert L.bw_version() >= 100
+
+
+def test_status_strings_and_argument_validation_need_no_gpu():
+    L = _lib.lib()
+    assert L.bw_status_string(0) == b"ok"
+    # validation happens before any CUDA call: bad bits, bad group, bad K, NULL pointers
+    z = None
+    assert L.bw_rtn_quantize_pack(z, 0, 4, 64, 3, 32, z, z, 0, z, 3, 0, z) == 1     # BW_ERR_BITS
+    assert L.bw_rtn_quantize_pack(z, 0, 4, 48, 4, 32, z, z, 0, z, 3, 0, z) == 2     # BW_ERR_GROUP
+    assert L.bw_rtn_quantize_pack(z, 0, 4, 12, 4, 4, z, z, 0, z, 3, 0, z) == 3      # K % 8 != 0
+    assert L.bw_rtn_quantize_pack(z, 7, 4, 64, 4, 32, z, z, 0, z, 3, 0, z) == 4     # BW_ERR_DTYPE
+    assert L.bw_rtn_quantize_pack(z, 0, 4, 64, 4, 32, z, z, 0, z, 3, 0, z) == 6     # BW_ERR_NULL
+    assert L.bw_rtn_quantize_pack(z, 0, 0, 64, 4, 32, z, z, 0, z, 3, 0, z) == 0     # empty is fine
+    assert L.bw_qmatmul(z, 1, 4, 8, 64, z, z, z, z, z, 1, 5, 32, z, 0, z) == 1
+    assert L.bw_qmatmul(z, 1, 4, 8, 64, z, z, z, z, z, 1, 4, 0, z, 0, z) == 2
+    assert L.bw_qmatmul(z, 1, 4, 8, 64, z, z, z, z, z, 1, 4, 32, z, 0, z) == 6
+    assert L.bw_qmatmul(z, 1, 0, 8, 64, z, z, z, z, z, 1, 4, 32, z, 0, z) == 0
+    assert L.bw_dequantize(z, z, 0, z, 3, 4, 64, 4, 32, z, 9, z) == 4
+    assert L.bw_qmatmul_workspace_bytes(16, 4096, 4096, 4, 128) == 0

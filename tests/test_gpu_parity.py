@@ -1,0 +1,338 @@
+"""GPU parity: the CUDA kernels, called through the C ABI (ctypes), against the golden
+fixtures produced by the reference and against the CPU oracle on identical seeded inputs.
+
+Bars: bit-exact for packed codes, zero-points, scales and dequantized weights; for matmul
+outputs max|err| <= 1e-2 * RMS(output) in 16-bit and <= 1e-5 relative in the fp32-accumulate
+checks (the tolerances the task states).
+"""
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from bitween_b200 import QuantizedLinear, dequantize_rtn, quantize_rtn, synth
+from bitween_b200.functional import quantize_rtn_to_module_buffers
+from bitween_b200.kernels import _lib
+from bitween_b200.kernels.cuda_loader import quantized_matmul_cuda, quantized_matmul_grad_input
+from helpers import ORACLE_DT, as_f32, assert_close_rms, from_bits, oracle_forward, rms, to_np
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+TORCH_DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+DEV = "cuda"
+
+
+def _golden(golden_dir, name):
+    return np.load(os.path.join(golden_dir, name))
+
+
+def _meta(golden_dir):
+    with open(os.path.join(golden_dir, "digests.json")) as f:
+        return json.load(f)
+
+
+def _w_tensor(arr, dt):
+    if dt == "f32":
+        return torch.from_numpy(arr.copy())
+    return from_bits(arr, TORCH_DT[dt])
+
+
+def _bits_equal(t, ref_np):
+    return to_np(t).tobytes() == np.ascontiguousarray(ref_np).tobytes()
+
+
+# --------------------------------------------------------------------------- RTN quantize
+
+def test_rtn_matches_reference_golden_bit_exact(golden_dir):
+    meta, gold = _meta(golden_dir), _golden(golden_dir, "rtn_small.npz")
+    for c in meta["rtn_meta"]:
+        n = c["name"]
+        w = _w_tensor(gold[n + "/w"], c["dtype"]).to(DEV)
+        q, s, z, g = quantize_rtn(w, bits=c["bits"], group_size=c["g"])
+        assert g == c["g"] and q.dtype == torch.int32 and z.dtype == torch.int32 and s.dtype == w.dtype
+        assert _bits_equal(q, gold[n + "/q"]), f"{n}: packed codes differ"
+        assert _bits_equal(z, gold[n + "/zp"]), f"{n}: zero points differ"
+        assert _bits_equal(s, gold[n + "/scale"]), f"{n}: scales differ"
+
+
+def test_rtn_cpu_tensor_round_trips_through_the_gpu(golden_dir):
+    gold = _golden(golden_dir, "rtn_small.npz")
+    w = torch.from_numpy(gold["rand_b4_g128_f32/w"].copy())
+    q, s, z, _ = quantize_rtn(w, bits=4, group_size=128)
+    assert q.device.type == "cpu" and _bits_equal(q, gold["rand_b4_g128_f32/q"])
+
+
+def _sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+def test_rtn_seeded_layers_match_reference_digests(golden_dir):
+    for name, c in _meta(golden_dir)["digests"].items():
+        w = torch.from_numpy(synth.normal(c["seed"], tuple(c["shape"]), c["std"]))
+        if c["dtype"] == "bf16->f32":
+            w = w.to(torch.bfloat16).to(torch.float32)
+        elif c["dtype"] != "f32":
+            w = w.to(TORCH_DT[c["dtype"]])
+        assert _sha(to_np(w)) == c["w_sha256"], name
+        q, s, z, _ = quantize_rtn(w.to(DEV), bits=c["bits"], group_size=c["g"])
+        assert _sha(to_np(q)) == c["q_sha256"], name
+        assert _sha(to_np(s)) == c["scale_sha256"], name
+        assert _sha(to_np(z)) == c["zp_sha256"], name
+        if c["dtype"] in ("f32", "bf16->f32"):
+            q2, s_h, z_h = quantize_rtn_to_module_buffers(w.to(DEV), c["bits"], c["g"])
+            assert _sha(to_np(q2)) == c["q_sha256"], name
+            assert _sha(to_np(s_h)) == c["scale_h_sha256"], name
+            assert _sha(to_np(z_h)) == c["zp_h_sha256"], name
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_rtn_vs_oracle_shapes_and_group_sizes(bits, dt):
+    vpi = 32 // bits
+    cases = [(1, 32, 32), (3, 64, 32), (7, 256, 64), (33, 384, 128), (130, 1024, 128), (257, 512, 256),
+             (5, 96, 16), (5, 96, 48), (9, 80, 8), (4, 64, 4), (3, 48, 24), (2, 2048, 2048), (2, 4096, 512),
+             (6, 32, 1), (1000, 128, 32)]
+    seed = 1000 * bits
+    for (N, K, g) in cases:
+        if K % vpi or K % g:
+            continue
+        seed += 1
+        w = torch.from_numpy(synth.normal(seed, (N, K), 0.05)).to(TORCH_DT[dt])
+        q, s, z, _ = quantize_rtn(w.to(DEV), bits=bits, group_size=g)
+        qo, so, zo = oracle.quantize_rtn(to_np(w), ORACLE_DT[w.dtype], bits, g)
+        assert _bits_equal(q, qo), (N, K, g, "codes")
+        assert _bits_equal(z, zo), (N, K, g, "zp")
+        assert _bits_equal(s, so), (N, K, g, "scale")
+
+
+def test_rtn_upcast_mode_equals_fp32_path():
+    w16 = torch.from_numpy(synth.normal(77, (64, 512), 0.02)).to(torch.bfloat16)
+    q, s_h, z_h = quantize_rtn_to_module_buffers(w16.to(DEV), 4, 128)
+    qo, so, zo = oracle.quantize_rtn(to_np(w16.float()), oracle.F32, 4, 128)
+    assert _bits_equal(q, qo)
+    assert _bits_equal(s_h, oracle.f16_bits(so))
+    assert _bits_equal(z_h, oracle.f16_bits(zo.astype(np.float32)))
+
+
+def test_rtn_error_bound_full_size_layer():
+    # size-independent property at a full Llama-3-8B shape: |w - dequant| <= scale/2 per element
+    torch.manual_seed(0)
+    w = (torch.randn(4096, 14336, device=DEV) * 0.02).to(torch.bfloat16).float()
+    for bits, g in ((4, 128), (8, 128), (2, 64)):
+        q, s, z, _ = quantize_rtn(w, bits=bits, group_size=g)
+        assert int(z.min()) >= 0 and int(z.max()) <= (1 << bits) - 1
+        d = dequantize_rtn(q, s, z, g, bits=bits)
+        err = (d - w).abs().view(4096, -1, g)
+        bound = s.view(4096, -1, 1) * 0.5 * (1 + 1e-5) + 1e-12
+        # elements clipped by the zero-point rounding may exceed scale/2 by at most one more half step
+        assert bool((err <= 2 * bound).all())
+        assert float((err <= bound).float().mean()) > 0.99
+        # idempotence: quantizing the dequantized weights reproduces the codes
+        q2, s2, z2, _ = quantize_rtn(d, bits=bits, group_size=g)
+        assert float((q2 == q).float().mean()) > 0.999
+
+
+# --------------------------------------------------------------------------- dequantize
+
+def test_dequantize_matches_reference_golden_bit_exact(golden_dir):
+    meta, gold = _meta(golden_dir), _golden(golden_dir, "rtn_small.npz")
+    for c in meta["rtn_meta"]:
+        n = c["name"]
+        q = torch.from_numpy(gold[n + "/q"].copy()).to(DEV)
+        s = _w_tensor(gold[n + "/scale"], c["dtype"]).to(DEV)
+        z = torch.from_numpy(gold[n + "/zp"].copy()).to(DEV)
+        d = dequantize_rtn(q, s, z, c["g"], bits=c["bits"])
+        assert d.dtype == torch.float32
+        assert _bits_equal(d, gold[n + "/deq"]), n
+
+
+def test_dequantize_module_dtypes_match_golden_fp16_weights(golden_dir):
+    meta, gold = _meta(golden_dir), _golden(golden_dir, "forward_small.npz")
+    for c in meta["fwd_meta"]:
+        n = c["name"]
+        q = torch.from_numpy(gold[n + "/q"].copy()).to(DEV)
+        s_h = from_bits(gold[n + "/scale_h"], torch.float16).to(DEV)
+        z_h = from_bits(gold[n + "/zp_h"], torch.float16).to(DEV)
+        w_h = dequantize_rtn(q, s_h, z_h, c["g"], bits=c["bits"], out_dtype=torch.float16)
+        assert _bits_equal(w_h, gold[n + "/w_h"]), n
+
+
+# --------------------------------------------------------------------------- qmatmul forward
+
+def test_forward_matches_reference_golden(golden_dir):
+    meta, gold = _meta(golden_dir), _golden(golden_dir, "forward_small.npz")
+    for c in meta["fwd_meta"]:
+        n = c["name"]
+        x = torch.from_numpy(gold[n + "/x"].copy()).to(DEV)              # fp32 in, cast inside
+        q = torch.from_numpy(gold[n + "/q"].copy()).to(DEV)
+        s_h = from_bits(gold[n + "/scale_h"], torch.float16).to(DEV)
+        z_h = from_bits(gold[n + "/zp_h"], torch.float16).to(DEV)
+        b_h = torch.from_numpy(gold[n + "/bias"].copy()).half().to(DEV) if c["bias"] else None
+        y = quantized_matmul_cuda(x, q, s_h, z_h, b_h, c["bits"], c["g"])
+        assert y.dtype == torch.float16 and tuple(y.shape) == (c["M"], c["N"])
+        ref = oracle.bits_to_f32(gold[n + "/y_h"], oracle.F16)
+        assert_close_rms(as_f32(y), ref, 1e-2, n)
+        # fp32-accumulate check against the fp64 sum of the same fp16 operands
+        acc = quantized_matmul_cuda(x, q, s_h, z_h, None, c["bits"], c["g"], out_dtype=torch.float32)
+        ref64 = gold[n + "/y_acc64"]
+        assert np.abs(as_f32(acc) - ref64).max() <= 1e-5 * np.abs(ref64).max(), n
+
+
+def _make_layer(seed, N, K, bits, g, bias):
+    w = torch.from_numpy(synth.normal(seed, (N, K), 0.02))
+    q, s, z = oracle.quantize_rtn(to_np(w), oracle.F32, bits, g)
+    q = torch.from_numpy(q)
+    s_h = torch.from_numpy(s).half()
+    z_h = torch.from_numpy(z).half()
+    b_h = torch.from_numpy(synth.normal(seed + 1, (N,), 0.02)).half() if bias else None
+    return q, s_h, z_h, b_h
+
+
+FWD_CASES = [
+    # bits, g, M, N, K, bias
+    (4, 128, 1, 256, 512, False), (4, 128, 2, 130, 384, True), (4, 128, 8, 64, 128, True),
+    (4, 128, 16, 768, 768, True), (4, 64, 5, 48, 192, False), (4, 32, 16, 100, 96, True),
+    (4, 16, 3, 40, 64, True), (4, 256, 9, 96, 1024, False), (4, 128, 16, 512, 4096, False),
+    (8, 128, 1, 128, 256, True), (8, 32, 16, 72, 160, False), (8, 8, 4, 24, 48, True),
+    (8, 64, 7, 200, 576, True), (8, 128, 16, 256, 2048, False),
+    (2, 64, 1, 64, 256, False), (2, 32, 16, 136, 192, True), (2, 128, 12, 80, 768, True),
+    (2, 64, 16, 256, 2048, False),
+    (4, 128, 17, 96, 256, True), (4, 128, 33, 64, 384, False), (8, 64, 64, 48, 256, True),
+    (2, 64, 50, 40, 512, True), (4, 64, 70, 20, 192, False), (4, 128, 200, 32, 256, True),
+    # layouts the streaming kernel cannot take -> general kernel
+    (4, 24, 4, 16, 96, True), (8, 12, 9, 8, 48, False), (2, 48, 3, 8, 96, True), (4, 8, 5, 12, 40, True),
+    (8, 4, 2, 6, 20, False), (4, 128, 3, 16, 128 * 3 + 0, True),
+]
+
+
+@pytest.mark.parametrize("case", FWD_CASES, ids=lambda c: "b%d_g%d_M%d_N%d_K%d_%s" % c)
+def test_forward_vs_oracle(case):
+    bits, g, M, N, K, bias = case
+    q, s_h, z_h, b_h = _make_layer(hash(case) % 100000, N, K, bits, g, bias)
+    x = torch.from_numpy(synth.normal(4242 + M, (M, K), 1.0)).half()
+    ref, ref_acc = oracle_forward(x, q, s_h, z_h, b_h, bits, g, want_acc=True)
+    dev = [t.to(DEV) if t is not None else None for t in (x, q, s_h, z_h, b_h)]
+    y = quantized_matmul_cuda(*dev, bits, g)
+    assert_close_rms(as_f32(y), as_f32(ref), 1e-2, str(case))
+    acc = quantized_matmul_cuda(dev[0], dev[1], dev[2], dev[3], None, bits, g, out_dtype=torch.float32)
+    denom = max(float(ref_acc.abs().max()), 1e-30)
+    assert float((acc.cpu() - ref_acc).abs().max()) <= 1e-5 * denom, case
+
+
+def test_forward_kernel_selection():
+    q, s_h, z_h, b_h = _make_layer(5, 64, 256, 4, 128, False)
+    x = torch.zeros(4, 256, dtype=torch.float16, device=DEV)
+    quantized_matmul_cuda(x, q.to(DEV), s_h.to(DEV), z_h.to(DEV), None, 4, 128)
+    assert _lib.last_qmatmul_kernel() == "qmm_smallm_kernel"
+    q, s_h, z_h, b_h = _make_layer(6, 16, 96, 4, 24, False)
+    x = torch.zeros(4, 96, dtype=torch.float16, device=DEV)
+    quantized_matmul_cuda(x, q.to(DEV), s_h.to(DEV), z_h.to(DEV), None, 4, 24)
+    assert _lib.last_qmatmul_kernel() == "qmm_general_kernel"
+
+
+@pytest.mark.parametrize("xdt", [torch.float32, torch.bfloat16])
+def test_forward_input_dtypes_are_cast_to_fp16_like_the_reference(xdt):
+    q, s_h, z_h, b_h = _make_layer(11, 96, 256, 4, 128, True)
+    x = torch.from_numpy(synth.normal(12, (6, 256), 1.0)).to(xdt)
+    ref = oracle_forward(x, q, s_h, z_h, b_h, 4, 128)            # casts x to fp16 (modules.py:74)
+    y = quantized_matmul_cuda(x.to(DEV), q.to(DEV), s_h.to(DEV), z_h.to(DEV), b_h.to(DEV), 4, 128)
+    assert y.dtype == torch.float16                               # always fp16 out (modules.py:106)
+    assert_close_rms(as_f32(y), as_f32(ref), 1e-2)
+
+
+def test_forward_bf16_output_extension():
+    q, s_h, z_h, b_h = _make_layer(13, 128, 512, 4, 128, False)
+    x = torch.from_numpy(synth.normal(14, (16, 512), 1.0)).to(torch.bfloat16)
+    # bf16 restatement of the reference: dequantize -> bf16 -> matmul, bf16 activations
+    ref = oracle_forward(x, q, s_h, z_h, None, 4, 128, act=torch.bfloat16)
+    y = quantized_matmul_cuda(x.to(DEV), q.to(DEV), s_h.to(DEV), z_h.to(DEV), None, 4, 128,
+                              out_dtype=torch.bfloat16)
+    assert y.dtype == torch.bfloat16
+    assert_close_rms(as_f32(y), as_f32(ref), 1e-2)
+
+
+def test_leading_dims_and_empty_batch():
+    q, s_h, z_h, b_h = _make_layer(15, 32, 128, 8, 32, True)
+    d = [t.to(DEV) for t in (q, s_h, z_h, b_h)]
+    x = torch.from_numpy(synth.normal(16, (2, 3, 128), 1.0)).half()
+    y = quantized_matmul_cuda(x.to(DEV), *d, 8, 32)
+    assert tuple(y.shape) == (2, 3, 32)
+    ref = oracle_forward(x.reshape(6, 128), q, s_h, z_h, b_h, 8, 32)
+    assert_close_rms(as_f32(y).reshape(6, 32), as_f32(ref), 1e-2)
+    y0 = quantized_matmul_cuda(torch.zeros(0, 128, dtype=torch.float16, device=DEV), *d, 8, 32)
+    assert tuple(y0.shape) == (0, 32)
+
+
+def test_config1_opt125m_qproj_end_to_end():
+    # 768 -> 768 with bias, fp32 weights, W4 g128, activations [16, 768] fp32
+    lin = torch.nn.Linear(768, 768, bias=True)
+    with torch.no_grad():
+        lin.weight.copy_(torch.from_numpy(synth.normal(1, (768, 768), 0.02)))
+        lin.bias.copy_(torch.from_numpy(synth.normal(2, (768,), 0.02)))
+    x = torch.from_numpy(synth.normal(3, (16, 768), 1.0))
+    ql = QuantizedLinear.from_float(lin.to(DEV), bits=4, group_size=128)
+    qo, so, zo = oracle.quantize_rtn(to_np(lin.weight.data.cpu()), oracle.F32, 4, 128)
+    assert _bits_equal(ql.qweight, qo)
+    assert _bits_equal(ql.scale, oracle.f16_bits(so))
+    assert _bits_equal(ql.zero_point, oracle.f16_bits(zo.astype(np.float32)))
+    assert _bits_equal(ql.bias, oracle.f16_bits(to_np(lin.bias.data.cpu())))
+    y = ql(x.to(DEV))
+    ref = oracle_forward(x, ql.qweight.cpu(), ql.scale.cpu(), ql.zero_point.cpu(), ql.bias.cpu(), 4, 128)
+    assert y.dtype == torch.float16 and tuple(y.shape) == (16, 768)
+    assert_close_rms(as_f32(y), as_f32(ref), 1e-2)
+
+
+@pytest.mark.parametrize("bits,g", [(4, 128), (8, 128)])
+@pytest.mark.parametrize("shape", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)])
+def test_decode_full_size_shapes_against_gpu_dequant_matmul(bits, g, shape):
+    # Llama-3-8B shapes: the fused kernel must agree with "dequantize (bit-exact kernel) then
+    # matmul" on the same device, and sampled rows must agree with the CPU oracle.
+    N, K = shape
+    gen = torch.Generator(device=DEV).manual_seed(N + K + bits)
+    w = (torch.randn(N, K, device=DEV, generator=gen) * 0.02).to(torch.bfloat16)
+    q, s_h, z_h = quantize_rtn_to_module_buffers(w, bits, g)
+    w_h = dequantize_rtn(q, s_h, z_h, g, bits=bits, out_dtype=torch.float16)
+    for M in (1, 2, 4, 8, 16):
+        x = torch.randn(M, K, device=DEV, generator=gen).to(torch.bfloat16)
+        y = quantized_matmul_cuda(x, q, s_h, z_h, None, bits, g)
+        ref = (x.half().float() @ w_h.float().T)
+        assert_close_rms(as_f32(y), as_f32(ref), 1e-2, f"{shape} M={M}")
+        acc = quantized_matmul_cuda(x, q, s_h, z_h, None, bits, g, out_dtype=torch.float32)
+        ref64 = x.half().double() @ w_h.double().T
+        assert float((acc.double() - ref64).abs().max()) <= 1e-5 * float(ref64.abs().max())
+    rows = torch.tensor([0, 1, 15, 16, N // 2 + 3, N - 1])
+    x = torch.randn(16, K, device=DEV, generator=gen).half()
+    y = quantized_matmul_cuda(x, q, s_h, z_h, None, bits, g)
+    ref = oracle_forward(x.cpu(), q[rows].cpu(), s_h[rows].cpu(), z_h[rows].cpu(), None, bits, g)
+    assert_close_rms(as_f32(y[:, rows]), as_f32(ref), 1e-2)
+
+
+# --------------------------------------------------------------------------- backward
+
+@pytest.mark.parametrize("bits,g,gdt", [(4, 128, torch.float16), (8, 32, torch.float32), (2, 64, torch.bfloat16),
+                                        (4, 24, torch.float32)])
+def test_grad_input_vs_oracle(bits, g, gdt):
+    N, K, M = 40, 384 if g != 24 else 96, 11
+    q, s_h, z_h, _ = _make_layer(900 + bits, N, K, bits, g, False)
+    go = torch.from_numpy(synth.normal(901, (M, N), 1.0)).to(gdt)
+    ref = oracle.qlinear_grad_input(to_np(go), ORACLE_DT[gdt], to_np(q), to_np(s_h), to_np(z_h), bits, g)
+    ref = torch.from_numpy(ref) if gdt == torch.float32 else from_bits(ref, gdt)
+    gi = quantized_matmul_grad_input(go.to(DEV), q.to(DEV), s_h.to(DEV), z_h.to(DEV), bits, g)
+    assert gi.dtype == gdt and tuple(gi.shape) == (M, K)
+    assert_close_rms(as_f32(gi), as_f32(ref), 1e-2 if gdt != torch.float32 else 1e-5)
+
+
+def test_autograd_through_quantized_linear():
+    lin = torch.nn.Linear(256, 64, bias=True).to(DEV)
+    ql = QuantizedLinear.from_float(lin, bits=4, group_size=64)
+    x = torch.randn(5, 256, device=DEV, dtype=torch.float16, requires_grad=True)
+    y = ql(x)
+    y.float().pow(2).sum().backward()
+    w = dequantize_rtn(ql.qweight, ql.scale, ql.zero_point, 64, bits=4)
+    ref = (2 * y.detach().float()).half().float() @ w
+    assert x.grad is not None and x.grad.dtype == torch.float16
+    assert_close_rms(as_f32(x.grad), as_f32(ref), 1e-2)

@@ -1,0 +1,134 @@
+"""Host-side mirror of the reference interface: argument rules, module state, the per-layer
+loop and the drop-in aliasing -- everything that needs no GPU."""
+import io
+import pickle
+from contextlib import redirect_stdout
+
+import pytest
+import torch
+import torch.nn as nn
+
+import bitween_b200
+from bitween_b200 import Bitween, QuantizedLinear, quantize_rtn
+from bitween_b200 import functional, modules
+from helpers import to_np
+from oracle import oracle
+
+
+def test_quantize_rtn_argument_errors_match_reference():
+    w = torch.zeros(4, 48)
+    with pytest.raises(ValueError, match="Padding 16 columns"):
+        quantize_rtn(w, bits=4, group_size=32)                 # functional.py:12-17
+    with pytest.raises(AssertionError, match="Only 2, 4, or 8-bit"):
+        quantize_rtn(w, bits=3, group_size=16)                 # functional.py:6
+    with pytest.raises(RuntimeError):
+        quantize_rtn(torch.zeros(4, 12), bits=4, group_size=4)  # 12 % 8 != 0: reference fails too
+
+
+def test_no_cpu_fallback():
+    if torch.cuda.is_available():
+        pytest.skip("CUDA present")
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        quantize_rtn(torch.zeros(4, 64), bits=4, group_size=32)
+    layer = QuantizedLinear(64, 8, bits=4, group_size=32)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        layer(torch.zeros(2, 64))
+
+
+def test_quantized_linear_state_matches_reference_layout():
+    m = QuantizedLinear(768, 256, bits=4, group_size=128, bias=True, dtype=torch.bfloat16)
+    sd = m.state_dict()
+    assert list(sd) == ["qweight", "scale", "zero_point", "bias"]
+    assert sd["qweight"].dtype == torch.int32 and tuple(sd["qweight"].shape) == (256, 96)
+    assert sd["scale"].dtype == torch.float16 and tuple(sd["scale"].shape) == (256, 6)
+    assert sd["zero_point"].dtype == torch.float16 and tuple(sd["zero_point"].shape) == (256, 6)
+    assert sd["bias"].dtype == torch.float16 and tuple(sd["bias"].shape) == (256,)
+    assert m.dtype == torch.float16                          # dtype arg is ignored (modules.py:167)
+    assert (m.in_features, m.out_features, m.bits, m.group_size, m.requires_grad) == (768, 256, 4, 128, False)
+    assert repr(m) == "QuantizedLinear(in_features=768, out_features=256, bias=True, bits=4, group_size=128)"
+    nb = QuantizedLinear(64, 8, bits=2, group_size=32, bias=False)
+    assert nb.bias is None and "bias" not in nb.state_dict()
+    assert tuple(nb.qweight.shape) == (8, 4)
+    with pytest.raises(ValueError, match="Only 2, 4, or 8 bits"):
+        QuantizedLinear(64, 8, bits=3)
+    with pytest.raises(ValueError, match="Group size"):
+        QuantizedLinear(64, 8, bits=4, group_size=0)
+
+
+def test_pickle_round_trip_and_bitween_alias():
+    m = QuantizedLinear(64, 8, bits=8, group_size=32)
+    m.qweight.fill_(7)
+    m2 = pickle.loads(pickle.dumps(m))
+    assert torch.equal(m2.qweight, m.qweight) and m2.bits == 8 and m2.group_size == 32
+    me = bitween_b200.install_as_bitween()
+    import bitween
+    import bitween.modules
+    from bitween.kernels.cuda_loader import quantized_matmul_cuda  # noqa: F401  (main.py:401)
+    from bitween.functional import quantize_rtn as q2, dequantize_rtn  # noqa: F401
+    assert bitween is me and bitween.modules.QuantizedLinear is QuantizedLinear and q2 is quantize_rtn
+
+
+def _oracle_from_float(layer, bits, group_size):
+    """from_float with the oracle doing the arithmetic (test double for the CUDA call)."""
+    w = layer.weight.data.float()
+    q, s, z = oracle.quantize_rtn(to_np(w), oracle.F32, bits, group_size)
+    ql = QuantizedLinear(layer.in_features, layer.out_features, bits, group_size, bias=layer.bias is not None)
+    ql.qweight.copy_(torch.from_numpy(q))
+    ql.scale.copy_(torch.from_numpy(s))
+    ql.zero_point.copy_(torch.from_numpy(z))
+    if layer.bias is not None:
+        ql.bias.data.copy_(layer.bias.data)
+    return ql
+
+
+class _Block(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.fc1 = nn.Linear(64, 128)
+        self.fc2 = nn.Linear(128, 64, bias=False)
+
+
+class _Tiny(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.embed_tokens = nn.Embedding(10, 64)
+        self.layers = nn.ModuleList([_Block(), _Block()])
+        self.lm_head = nn.Linear(64, 10, bias=False)
+
+
+def test_bitween_rtn_loop_replaces_linears(monkeypatch):
+    monkeypatch.setattr(QuantizedLinear, "from_float", classmethod(
+        lambda cls, layer, bits=8, group_size=32: _oracle_from_float(layer, bits, group_size)))
+    model = _Tiny()
+    buf = io.StringIO()
+    with redirect_stdout(buf):
+        qm = Bitween(model, bits=4, group_size=32).quantize(rtn=True, ignore_layers=["lm_head"])
+    out = buf.getvalue()
+    assert "  - Quantizing layer: layers.0.fc1" in out and "  - Skipping ignored layer: lm_head" in out
+    assert "--- Quantization complete ---" in out
+    assert isinstance(qm.layers[0].fc1, QuantizedLinear) and isinstance(qm.layers[1].fc2, QuantizedLinear)
+    assert isinstance(qm.lm_head, nn.Linear)
+    assert isinstance(model.layers[0].fc1, nn.Linear), "the original model must stay untouched"
+    assert qm.layers[1].fc2.bias is None and qm.layers[0].fc1.bias.dtype == torch.float16
+    assert tuple(qm.layers[0].fc1.qweight.shape) == (128, 8)
+    # layer_filter keeps only every second layer (multi-GPU layer sharding hook)
+    with redirect_stdout(io.StringIO()):
+        half = Bitween(model, bits=4, group_size=32).quantize(
+            rtn=True, ignore_layers=["lm_head"], layer_filter=lambda i, name: i % 2 == 0)
+    kinds = [type(m).__name__ for m in (half.layers[0].fc1, half.layers[0].fc2, half.layers[1].fc1, half.layers[1].fc2)]
+    assert kinds == ["QuantizedLinear", "Linear", "QuantizedLinear", "Linear"]
+    with pytest.raises(NotImplementedError):
+        Bitween(model).quantize(trainable=True)
+    with pytest.raises(AssertionError):
+        Bitween(model, group_size=0)
+
+
+def test_qmatmul_wrapper_validates_before_crossing_abi():
+    from bitween_b200.kernels.cuda_loader import quantized_matmul_cuda
+    x = torch.zeros(2, 64, dtype=torch.float16)
+    with pytest.raises(ValueError):
+        quantized_matmul_cuda(x, torch.zeros(8, 8, dtype=torch.int32), None, None, None, 3, 32)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        quantized_matmul_cuda(x, torch.zeros(8, 8, dtype=torch.int32), torch.zeros(8, 2), torch.zeros(8, 2),
+                              None, 4, 32)
+    assert functional.quantize_rtn is quantize_rtn and modules.QuantizedLinear is QuantizedLinear
