@@ -179,6 +179,26 @@ __device__ __forceinline__ void load_unit(const XT *src, bool valid, __half (&h)
     for (int i = 0; i < UNIT; ++i) h[i] = x_to_half<XT>(tmp[i]);
 }
 
+// (lo16 of x, lo16 of y) and (hi16 of x, hi16 of y)
+__device__ __forceinline__ uint32_t pair_lo(uint32_t x, uint32_t y) { return __byte_perm(x, y, 0x5410); }
+__device__ __forceinline__ uint32_t pair_hi(uint32_t x, uint32_t y) { return __byte_perm(x, y, 0x7632); }
+
+template <typename XT> __device__ __forceinline__ uint32_t pair_to_half2(uint32_t raw);
+template <> __device__ __forceinline__ uint32_t pair_to_half2<__half>(uint32_t raw) { return raw; }
+template <> __device__ __forceinline__ uint32_t pair_to_half2<__nv_bfloat16>(uint32_t raw) {
+    return h2_as_u32(__floats2half2_rn(__uint_as_float(raw << 16), __uint_as_float(raw & 0xffff0000u)));
+}
+
+// Shared-memory slot (in uint4 units) of activation piece `px` of lane column `t`, token m.
+template <int BITS, int MT>
+__device__ __forceinline__ int x_slot(int cl, int px, int m, int t) {
+    return ((cl * Geometry<BITS>::NX + px) * MT + (m >> 3)) * 32 + (m & 7) * 4 + t;
+}
+
+// Stages the activations of k-chunks [chunk0, chunk0+nchunks) and the per-(group,row)
+// constants.  16-bit activations go global->shared with cp.async (all copies of a thread in
+// flight at once) and are converted/permuted in place by the thread that copied them; fp32
+// activations take a batched register path.
 template <int BITS, int MT, int RT, int WARPS, bool TWO_GROUPS, typename XT>
 __device__ __forceinline__ void stage_block(const SmallMParams &p, int chunk0, int nchunks, int n0,
                                             uint4 *xs, GroupConst *gc, int grp0, int ngrp) {
@@ -186,52 +206,124 @@ __device__ __forceinline__ void stage_block(const SmallMParams &p, int chunk0, i
     constexpr int UNIT = Geo::UNIT;
     constexpr int ROWS = WARPS * RT * 16;
     constexpr int MTOK = MT * 8;
-    const int tid = threadIdx.x;
     constexpr int NTHR = WARPS * 32;
+    constexpr int UPC = Geo::KC / UNIT;                  // staging units per chunk
+    const int tid = threadIdx.x;
     const XT *x = reinterpret_cast<const XT *>(p.x);
-    // --- activations ---
-    const int units_per_chunk = Geo::KC / UNIT;
-    const int total_units = nchunks * units_per_chunk * MTOK;
-    for (int i = tid; i < total_units; i += NTHR) {
-        const int u = i % (nchunks * units_per_chunk);   // unit along k (fastest => coalesced)
-        const int m = i / (nchunks * units_per_chunk);   // token
-        const int cl = u / units_per_chunk;
-        const int uc = u % units_per_chunk;
-        const int64_t k = (int64_t)(chunk0 + cl) * Geo::KC + (int64_t)uc * UNIT;
-        __half h[UNIT];
-        load_unit<UNIT, XT>(x + (int64_t)m * p.K + k, (m < p.M) && (k < p.K), h);
-        const int mt = m >> 3, g = m & 7;
+    const int upr = nchunks * UPC;                       // units per token row (k fastest => coalesced)
+    const int total_units = upr * MTOK;
+
+    // decode unit index -> (token, chunk, unit-in-chunk); slots of its one or two pieces
+    auto slots_of = [&](int i, int &m, int64_t &k, int &s0, int &s1) {
+        const int u = i % upr;
+        m = i / upr;
+        const int cl = u / UPC, uc = u % UPC;
+        k = (int64_t)(chunk0 + cl) * Geo::KC + (int64_t)uc * UNIT;
+        if constexpr (BITS == 4) { s0 = x_slot<BITS, MT>(cl, uc & 3, m, uc >> 2); s1 = s0; }
+        else if constexpr (BITS == 8) { s0 = x_slot<BITS, MT>(cl, uc & 1, m, uc >> 1); s1 = s0; }
+        else { s0 = x_slot<BITS, MT>(cl, 2 * (uc & 3), m, uc >> 2); s1 = x_slot<BITS, MT>(cl, 2 * (uc & 3) + 1, m, uc >> 2); }
+    };
+    auto permute_store = [&](const uint32_t (&r)[UNIT / 2], int s0, int s1) {
         if constexpr (BITS == 4) {
-            const int t = uc >> 2, px = uc & 3;           // word uc of the chunk: lane column t, word px
-            alignas(16) __half o[8] = {h[0], h[4], h[1], h[5], h[2], h[6], h[3], h[7]};
-            xs[((cl * Geo::NX + px) * MT + mt) * 32 + g * 4 + t] = *reinterpret_cast<uint4 *>(o);
+            xs[s0] = make_uint4(pair_lo(r[0], r[2]), pair_hi(r[0], r[2]), pair_lo(r[1], r[3]), pair_hi(r[1], r[3]));
         } else if constexpr (BITS == 8) {
-            const int t = uc >> 1, px = uc & 1;           // two words per 16-byte piece
-            alignas(16) __half o[8] = {h[0], h[2], h[1], h[3], h[4], h[6], h[5], h[7]};
-            xs[((cl * Geo::NX + px) * MT + mt) * 32 + g * 4 + t] = *reinterpret_cast<uint4 *>(o);
+            xs[s0] = make_uint4(pair_lo(r[0], r[1]), pair_hi(r[0], r[1]), pair_lo(r[2], r[3]), pair_hi(r[2], r[3]));
         } else {
-            const int t = uc >> 2, wi = uc & 3;           // one 16-code word -> two pieces
-            alignas(16) __half o0[8] = {h[0], h[8], h[1], h[9], h[2], h[10], h[3], h[11]};
-            alignas(16) __half o1[8] = {h[4], h[12], h[5], h[13], h[6], h[14], h[7], h[15]};
-            xs[((cl * Geo::NX + 2 * wi) * MT + mt) * 32 + g * 4 + t] = *reinterpret_cast<uint4 *>(o0);
-            xs[((cl * Geo::NX + 2 * wi + 1) * MT + mt) * 32 + g * 4 + t] = *reinterpret_cast<uint4 *>(o1);
+            xs[s0] = make_uint4(pair_lo(r[0], r[4]), pair_hi(r[0], r[4]), pair_lo(r[1], r[5]), pair_hi(r[1], r[5]));
+            xs[s1] = make_uint4(pair_lo(r[2], r[6]), pair_hi(r[2], r[6]), pair_lo(r[3], r[7]), pair_hi(r[3], r[7]));
+        }
+    };
+
+    if constexpr (sizeof(XT) == 2) {
+        for (int i = tid; i < total_units; i += NTHR) {
+            int m, s0, s1; int64_t k;
+            slots_of(i, m, k, s0, s1);
+            const bool valid = (m < p.M) && (k < p.K);
+            const XT *src = x + (valid ? ((int64_t)m * p.K + k) : 0);
+            cp_async16(xs + s0, src, valid);
+            if constexpr (UNIT == 16) cp_async16(xs + s1, src + 8, valid);
+        }
+        cp_async_commit();
+    }
+
+    // --- per-(group,row) constants, loads batched four at a time ---
+    const int total_gc = ngrp * ROWS;
+    for (int base = tid; base < total_gc; base += NTHR * 4) {
+        __half sv[4], zv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = base + j * NTHR;
+            if (i < total_gc) {
+                const int gl = i % ngrp, r = i / ngrp;
+                int64_t n = (int64_t)n0 + r;
+                if (n >= p.N) n = p.N - 1;
+                int grp = grp0 + gl;
+                if (grp >= p.G) grp = p.G - 1;
+                sv[j] = p.scale[n * p.G + grp];
+                zv[j] = p.zp[n * p.G + grp];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = base + j * NTHR;
+            if (i < total_gc) {
+                const int gl = i % ngrp, r = i / ngrp;
+                GroupConst c;
+                c.s2 = h2_as_u32(__half2half2(sv[j]));
+                c.z1024 = h2_as_u32(__hadd2(__half2half2(zv[j]), __float2half2_rn(1024.0f)));
+                gc[gl * ROWS + r] = c;
+            }
         }
     }
-    // --- per-(group,row) constants ---
-    const int total_gc = ngrp * ROWS;
-    for (int i = tid; i < total_gc; i += NTHR) {
-        const int gl = i % ngrp;
-        const int r = i / ngrp;
-        int64_t n = (int64_t)n0 + r;
-        if (n >= p.N) n = p.N - 1;
-        int grp = grp0 + gl;
-        if (grp >= p.G) grp = p.G - 1;
-        const __half s = p.scale[n * p.G + grp];
-        const __half z = p.zp[n * p.G + grp];
-        GroupConst c;
-        c.s2 = h2_as_u32(__half2half2(s));
-        c.z1024 = h2_as_u32(__hadd2(__half2half2(z), __float2half2_rn(1024.0f)));
-        gc[gl * ROWS + r] = c;
+
+    if constexpr (sizeof(XT) == 2) {
+        cp_async_wait<0>();   // this thread's own copies (and its weight prefetches) have landed
+        for (int i = tid; i < total_units; i += NTHR) {
+            int m, s0, s1; int64_t k;
+            slots_of(i, m, k, s0, s1);
+            uint32_t r[UNIT / 2];
+            const uint4 a = xs[s0];
+            r[0] = pair_to_half2<XT>(a.x); r[1] = pair_to_half2<XT>(a.y);
+            r[2] = pair_to_half2<XT>(a.z); r[3] = pair_to_half2<XT>(a.w);
+            if constexpr (UNIT == 16) {
+                const uint4 b = xs[s1];
+                r[4] = pair_to_half2<XT>(b.x); r[5] = pair_to_half2<XT>(b.y);
+                r[6] = pair_to_half2<XT>(b.z); r[7] = pair_to_half2<XT>(b.w);
+            }
+            permute_store(r, s0, s1);
+        }
+    } else {
+        // fp32 activations: rounded to fp16 (bitween/modules.py:74), two units per batch
+        for (int base = tid; base < total_units; base += NTHR * 2) {
+            float v[2][UNIT];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int i = base + j * NTHR;
+                int m, s0, s1; int64_t k;
+                if (i < total_units) {
+                    slots_of(i, m, k, s0, s1);
+                    const bool valid = (m < p.M) && (k < p.K);
+                    const float4 *src = reinterpret_cast<const float4 *>(x + (valid ? ((int64_t)m * p.K + k) : 0));
+#pragma unroll
+                    for (int e = 0; e < UNIT / 4; ++e) {
+                        const float4 f = valid ? __ldg(src + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        v[j][4 * e] = f.x; v[j][4 * e + 1] = f.y; v[j][4 * e + 2] = f.z; v[j][4 * e + 3] = f.w;
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int i = base + j * NTHR;
+                if (i < total_units) {
+                    int m, s0, s1; int64_t k;
+                    slots_of(i, m, k, s0, s1);
+                    uint32_t r[UNIT / 2];
+#pragma unroll
+                    for (int e = 0; e < UNIT / 2; ++e) r[e] = h2_as_u32(__floats2half2_rn(v[j][2 * e], v[j][2 * e + 1]));
+                    permute_store(r, s0, s1);
+                }
+            }
+        }
     }
 }
 
