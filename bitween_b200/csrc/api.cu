@@ -26,9 +26,11 @@ int dequantize(const int32_t *q, const void *scale, int scale_dtype, const void 
                int64_t N, int64_t K, int bits, int g, void *out, int out_dtype, cudaStream_t st);
 int qmatmul_smallm(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
                    const __half *scale, const __half *zp, const __half *bias, void *out, int out_dtype,
-                   int bits, int g, cudaStream_t st);
+                   int bits, int g, void *workspace, cudaStream_t st);
 bool smallm_fast_path_ok(const void *x, int x_dtype, int64_t K, const int32_t *q, int bits, int g);
+size_t smallm_workspace_bytes(int64_t M, int64_t K, int bits);
 void set_smallm_tuning(int rt, int warps, int splits);
+void set_smallm_pdl(int on);
 int qmatmul_grad_input(const void *go, int dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
                        const __half *scale, const __half *zp, void *gi, int bits, int g, cudaStream_t st);
 
@@ -73,8 +75,14 @@ int bw_dequantize(const int32_t *qweight, const void *scale, int scale_dtype, co
 }
 
 size_t bw_qmatmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int bits, int group_size) {
-    (void)M; (void)N; (void)K; (void)bits; (void)group_size;
-    return 0;  // split-K sums travel through distributed shared memory; no global scratch
+    // The streaming kernel reads activations that a preparation kernel has cast to fp16 and
+    // laid out in tensor-core fragment order: K (rounded up to a k-chunk) x 8*ceil(M/8) x 2
+    // bytes for one block of at most 64 tokens.  Split-K sums travel through distributed
+    // shared memory and need no global scratch.
+    (void)N; (void)group_size;
+    if (bits != 2 && bits != 4 && bits != 8) return 0;
+    if (M <= 0 || K <= 0) return 0;
+    return smallm_workspace_bytes(M < 64 ? M : 64, K, bits);
 }
 
 int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *qweight,
@@ -91,22 +99,22 @@ int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
         !aligned_to(qweight, 4) || !aligned_to(scale, 2) || !aligned_to(zero_point, 2) ||
         !aligned_to(bias, 2))
         return BW_ERR_ALIGN;
-    if (workspace_bytes < bw_qmatmul_workspace_bytes(M, N, K, bits, group_size)) return BW_ERR_WORKSPACE;
-    (void)workspace;
     cudaStream_t st = (cudaStream_t)stream;
     const __half *s = (const __half *)scale, *z = (const __half *)zero_point, *b = (const __half *)bias;
     if (K == 0) {
         // empty reduction: out = bias (or 0); run the general kernel, which handles it
-        return qmatmul_smallm(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, st);
+        return qmatmul_smallm(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, nullptr, st);
     }
     if (!smallm_fast_path_ok(x, x_dtype, K, qweight, bits, group_size))
-        return qmatmul_smallm(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, st);
+        return qmatmul_smallm(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, nullptr, st);
+    if (!workspace || workspace_bytes < bw_qmatmul_workspace_bytes(M, N, K, bits, group_size))
+        return BW_ERR_WORKSPACE;
     // token blocks of at most 64 through the streaming kernel
     const size_t xs = dtype_size(x_dtype), os = dtype_size(out_dtype);
     for (int64_t m0 = 0; m0 < M; m0 += 64) {
         const int64_t mc = (M - m0 < 64) ? (M - m0) : 64;
         rc = qmatmul_smallm((const char *)x + (size_t)m0 * K * xs, x_dtype, mc, N, K, qweight, s, z, b,
-                            (char *)out + (size_t)m0 * N * os, out_dtype, bits, group_size, st);
+                            (char *)out + (size_t)m0 * N * os, out_dtype, bits, group_size, workspace, st);
         if (rc != BW_OK) return rc;
     }
     return BW_OK;
@@ -174,5 +182,6 @@ const char *bw_last_qmatmul_kernel(void) { return g_last_kernel; }
 
 // Not in the public header: tuning hook used by the benchmark's sweep mode.
 BW_API void bw_debug_set_smallm_tuning(int rt, int warps, int splits) { set_smallm_tuning(rt, warps, splits); }
+BW_API void bw_debug_set_pdl(int on) { set_smallm_pdl(on); }
 
 }  // extern "C"

@@ -16,7 +16,8 @@ RTN_UPCAST_F32 = 1
 _DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int32: I32}
 
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIB_PATH = os.path.join(_PKG, "_C", "libbitween_b200.so")
+# BITWEEN_B200_LIB points at an alternative build of the same library (kernel experiments).
+LIB_PATH = os.environ.get("BITWEEN_B200_LIB") or os.path.join(_PKG, "_C", "libbitween_b200.so")
 
 _lib = None
 _lock = threading.Lock()
@@ -62,6 +63,8 @@ def _declare(L):
     L.bw_version.restype = i32
     L.bw_debug_set_smallm_tuning.argtypes = [i32, i32, i32]
     L.bw_debug_set_smallm_tuning.restype = None
+    L.bw_debug_set_pdl.argtypes = [i32]
+    L.bw_debug_set_pdl.restype = None
 
 
 def lib():
@@ -106,6 +109,27 @@ def stream_ptr(device):
 
 def ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+_workspaces = {}
+_retired = []
+
+
+def workspace(device, nbytes):
+    """Caller-owned scratch for bw_qmatmul, cached per (device, stream): calls that may overlap on
+    the GPU must not share scratch, and calls on one stream are ordered.  The buffer only grows;
+    it is never freed while the process lives, so pointers captured in CUDA graphs stay valid
+    as long as the first capture already saw the largest size it needs."""
+    if nbytes == 0:
+        return None
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            _retired.append(buf)   # a captured CUDA graph may still hold its address
+        buf = torch.empty(max(nbytes, 1 << 21), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
 
 
 def last_qmatmul_kernel():

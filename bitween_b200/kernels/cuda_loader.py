@@ -68,9 +68,12 @@ def quantized_matmul_cuda(x, qweight, scale, zero_point, bias, bits, group_size,
             raise ValueError("`out` must be a contiguous [M, N] tensor of out_dtype on x's device")
     L = _lib.lib()
     with torch.cuda.device(dev):
+        ws_bytes = L.bw_qmatmul_workspace_bytes(M, N, K, bits, group_size)
+        ws = _lib.workspace(dev, ws_bytes)
         rc = L.bw_qmatmul(_lib.ptr(x2), _lib.dtype_code(x2.dtype), M, N, K, _lib.ptr(qweight),
                           _lib.ptr(scale), _lib.ptr(zero_point), _lib.ptr(bias), _lib.ptr(out),
-                          _lib.dtype_code(out_dtype), bits, group_size, None, 0, _lib.stream_ptr(dev))
+                          _lib.dtype_code(out_dtype), bits, group_size, _lib.ptr(ws),
+                          0 if ws is None else ws.numel(), _lib.stream_ptr(dev))
     _lib.check(rc)
     return out.reshape(*x.shape[:-1], N)
 
@@ -123,9 +126,11 @@ def quantized_matmul_host(x_host, qweight, scale, zero_point, bias, bits, group_
     dev = x_dev.device
     L = _lib.lib()
     with torch.cuda.device(dev):
+        ws = _lib.workspace(dev, L.bw_qmatmul_workspace_bytes(M, N, K, bits, group_size))
         rc = L.bw_qmatmul_host(_lib.ptr(x_host), _lib.dtype_code(x_host.dtype), M, N, K, _lib.ptr(qweight),
                                _lib.ptr(scale), _lib.ptr(zero_point), _lib.ptr(bias), _lib.ptr(out_host),
                                _lib.dtype_code(out_host.dtype), bits, group_size, _lib.ptr(x_dev),
-                               _lib.ptr(out_dev), None, 0, _lib.stream_ptr(dev))
+                               _lib.ptr(out_dev), _lib.ptr(ws), 0 if ws is None else ws.numel(),
+                               _lib.stream_ptr(dev))
     _lib.check(rc)
     return out_host

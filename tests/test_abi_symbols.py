@@ -41,4 +41,6 @@ def test_status_strings_and_argument_validation_need_no_gpu():
     assert L.bw_qmatmul(z, 1, 4, 8, 64, z, z, z, z, z, 1, 4, 32, z, 0, z) == 6
     assert L.bw_qmatmul(z, 1, 0, 8, 64, z, z, z, z, z, 1, 4, 32, z, 0, z) == 0
     assert L.bw_dequantize(z, z, 0, z, 3, 4, 64, 4, 32, z, 9, z) == 4
-    assert L.bw_qmatmul_workspace_bytes(16, 4096, 4096, 4, 128) == 0
+    assert L.bw_qmatmul_workspace_bytes(16, 4096, 4096, 4, 128) == 4096 * 16 * 2
+    assert L.bw_qmatmul_workspace_bytes(1, 4096, 100, 4, 4) == 8 * 128 * 2
+    assert L.bw_qmatmul_workspace_bytes(0, 8, 64, 4, 32) == 0
