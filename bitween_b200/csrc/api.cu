@@ -31,6 +31,9 @@ bool smallm_fast_path_ok(const void *x, int x_dtype, int64_t K, const int32_t *q
 size_t smallm_workspace_bytes(int64_t M, int64_t K, int bits);
 void set_smallm_tuning(int rt, int warps, int splits);
 void set_smallm_pdl(int on);
+int rtn_device_status();
+void set_rtn_stream(int on);
+long long div_self_check(unsigned long long n, unsigned long long seed);
 int qmatmul_grad_input(const void *go, int dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
                        const __half *scale, const __half *zp, void *gi, int bits, int g, cudaStream_t st);
 
@@ -177,11 +180,22 @@ const char *bw_status_string(int status) {
 }
 
 const char *bw_last_cuda_error(void) { return g_cuda_error; }
+
+int bw_device_status(void) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return record_cuda_error(cudaGetLastError(), "cudaDeviceSynchronize");
+    const int v = rtn_device_status();
+    if (v < 0) return BW_ERR_CUDA;
+    return v ? BW_ERR_TIMEOUT : BW_OK;
+}
 int bw_version(void) { return 100; }
 const char *bw_last_qmatmul_kernel(void) { return g_last_kernel; }
 
 // Not in the public header: tuning hook used by the benchmark's sweep mode.
 BW_API void bw_debug_set_smallm_tuning(int rt, int warps, int splits) { set_smallm_tuning(rt, warps, splits); }
 BW_API void bw_debug_set_pdl(int on) { set_smallm_pdl(on); }
+BW_API void bw_debug_set_rtn_stream(int on) { set_rtn_stream(on); }
+// Test hook (allocates a counter; not for production callers): mismatches between the RTN
+// kernel's reciprocal-based division and IEEE division over n operand pairs.
+BW_API long long bw_debug_div_self_check(unsigned long long n, unsigned long long seed) { return div_self_check(n, seed); }
 
 }  // extern "C"

@@ -6,11 +6,12 @@
 // plus an int32 temporary -- by ONE pass: each weight is read once, codes are packed in
 // registers and only the packed words, scales and zero-points are written.
 //
-// Bit-exactness: every arithmetic step uses the correctly rounded IEEE intrinsic
-// (__fsub_rn, __fdiv_rn, __fadd_rn, rintf) in the order torch evaluates the expression,
-// with an extra rounding to the tensor dtype after each step when the weights are
-// fp16/bf16 and "native" arithmetic is requested (torch computes 16-bit elementwise ops
-// in fp32 and rounds the result back).  No fast-math, no reciprocal, no FMA contraction.
+// Bit-exactness: every arithmetic step produces the correctly rounded IEEE result in the
+// order torch evaluates the expression (__fsub_rn, __fdiv_rn, __fadd_rn, rintf, or a
+// provably equivalent form -- see the fast path below), with an extra rounding to the
+// tensor dtype after each step when the weights are fp16/bf16 and "native" arithmetic is
+// requested (torch computes 16-bit elementwise ops in fp32 and rounds the result back).
+// No fast-math, no approximate reciprocal, no FMA contraction.
 //
 // Data layout: weights are read as 16-byte vectors, lane-contiguous, so a warp
 // instruction covers 512 contiguous bytes; a quantization group occupies g/V
@@ -66,6 +67,26 @@ template <> __device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfl
     }
 }
 
+// 16 bytes already in registers -> fp32 elements
+template <typename T> __device__ __forceinline__ void unpack16(const uint4 &v, float (&out)[Elems16<T>::V]);
+template <> __device__ __forceinline__ void unpack16<float>(const uint4 &v, float (&out)[4]) {
+    out[0] = __uint_as_float(v.x); out[1] = __uint_as_float(v.y);
+    out[2] = __uint_as_float(v.z); out[3] = __uint_as_float(v.w);
+}
+template <> __device__ __forceinline__ void unpack16<__half>(const uint4 &v, float (&out)[8]) {
+    const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 f = __half22float2(h[i]); out[2 * i] = f.x; out[2 * i + 1] = f.y; }
+}
+template <> __device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4 &v, float (&out)[8]) {
+    const uint32_t *u = reinterpret_cast<const uint32_t *>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        out[2 * i] = __uint_as_float(u[i] << 16);
+        out[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+}
+
 template <typename ZT> __device__ __forceinline__ void store_zp(ZT *p, int32_t z);
 template <> __device__ __forceinline__ void store_zp<int32_t>(int32_t *p, int32_t z) { *p = z; }
 template <> __device__ __forceinline__ void store_zp<__half>(__half *p, int32_t z) { *p = __int2half_rn(z); }
@@ -92,18 +113,147 @@ __device__ __forceinline__ uint32_t code_of(float v, float s, float zf, float qm
 }
 
 // ---- fast path: g = V * 2^j, g/V <= 32 -------------------------------------------------
+//
+// Per-element arithmetic on the common path (finite weights, scale within 2^-40..2^40):
+//   * w/scale: the correctly rounded fp32 quotient torch computes, obtained from one
+//     correctly rounded reciprocal per group and four FMAs per element (div_by_recip).
+//   * round-half-even + clamp + int conversion: clamp(rint(t),0,Q) == rint(clamp(t,0,Q)), and
+//     for 0 <= t <= 255 the sum t + 1.5*2^23 is rounded to an integer by the fp32 adder itself
+//     (half-to-even), leaving the code in the low mantissa bits.
+// Groups with a NaN/Inf weight or an out-of-range scale take the step-by-step path below,
+// which mirrors torch's NaN/Inf propagation (bitween/functional.py:25-29 on such inputs).
+// Correctly rounded fp32 quotient v/s from the correctly rounded reciprocal r = RN(1/s)
+// (one __frcp_rn per group) with fused multiply-adds only:
+//   q0 = RN(v*r)                      within 1.5 ulp of v/s
+//   q1 = RN(q0 + RN(v - s*q0) * r)    a faithful rounding (error <= 1/2 ulp + 2^-22 ulp)
+//   q2 = RN(q1 + (v - s*q1) * r)      the residual of a faithful quotient is exact, and
+//                                     Markstein's theorem (correction of a faithful quotient
+//                                     with the correctly rounded reciprocal) gives RN(v/s)
+// Valid for normal operands without over/underflow: the caller guarantees |v| <= 2^40 and
+// 2^-40 <= s <= 2^40.  For |v| < 2^-79 the residual may underflow, but then |v/s| < 2^-39 and
+// the code does not depend on the quotient's low bits (adding the integer zero-point absorbs
+// it).  tests/test_gpu_parity.py compares this against __fdiv_rn on 2^28 operand pairs.
+__device__ __forceinline__ float div_by_recip(float v, float s, float r) {
+    const float q0 = __fmul_rn(v, r);
+    const float q1 = __fmaf_rn(__fmaf_rn(-s, q0, v), r, q0);
+    return __fmaf_rn(__fmaf_rn(-s, q1, v), r, q1);
+}
+
+// One 16-byte chunk per lane: group min/max over the lane segment, group parameters, codes,
+// packed words and the group's scale / zero-point.  `c` is the global chunk index of this lane.
+template <typename T, bool NATIVE, int BITS, typename ST, typename ZT>
+__device__ __forceinline__ void rtn_slot(float (&v)[Elems16<T>::V], int64_t c, bool in_range, int lane, int cpg,
+                                         int cpg_log2, uint32_t seg_mask, float floor_s,
+                                         int32_t *__restrict__ qweight, ST *__restrict__ scale,
+                                         ZT *__restrict__ zp) {
+    constexpr int V = Elems16<T>::V;
+    constexpr int VPI = 32 / BITS;
+    constexpr float QMAX = (float)((1 << BITS) - 1);
+    constexpr float MAGIC = 12582912.0f;                 // 1.5 * 2^23
+    constexpr uint32_t MAGIC_BITS = 0x4B400000u;
+    float mn = v[0], mx = v[0];
+    // NaN/Inf detector on the (otherwise idle) FMA pipe: a sum is NaN or Inf as soon as one
+    // addend is; a sum of finite values that overflows only sends the group down the slow,
+    // still exact, path.  fminf/fmaxf drop NaNs, so they cannot serve as the detector.
+    float sum = v[0];
+#pragma unroll
+    for (int j = 1; j < V; ++j) {
+        mn = fminf(mn, v[j]);
+        mx = fmaxf(mx, v[j]);
+        sum = __fadd_rn(sum, v[j]);
+    }
+    for (int off = cpg >> 1; off > 0; off >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    }
+    // bad: a NaN/Inf in this lane's elements, or a weight beyond +-2^40 in the group
+    const bool bad = !(fabsf(sum) <= 3.0e38f) || !(mn >= -1.0995116e12f) || !(mx <= 1.0995116e12f);
+    const bool group_bad = (__ballot_sync(0xffffffffu, bad) & seg_mask) != 0u;
+    float s, zf; int32_t zi;
+    uint32_t words[V >= VPI ? V / VPI : 1];
+    bool fast = !group_bad;
+    if (fast) {
+        group_params<T, NATIVE>(mn, mx, QMAX, floor_s, s, zi, zf);
+        fast = (s >= 9.094947e-13f) && (s <= 1.0995116e12f);   // 2^-40 <= scale <= 2^40
+    }
+    if (fast) {
+        const float r = __frcp_rn(s);
+        const int pos0 = (V >= VPI) ? 0 : (lane & (VPI / V - 1)) * V;
+#pragma unroll
+        for (int wi = 0; wi < (V >= VPI ? V / VPI : 1); ++wi) {
+            // word = sum_i code_i * 2^(pos_i*bits); the codes arrive as MAGIC_BITS + code_i, so
+            // one integer multiply-add per element accumulates them and the constant
+            // MAGIC_BITS * sum_i 2^(pos_i*bits) is removed once at the end (mod 2^32).
+            uint32_t acc = 0, bias = 0;
+#pragma unroll
+            for (int i = 0; i < (V >= VPI ? VPI : V); ++i) {
+                const float x = v[wi * VPI + i];
+                float t = rnd<T, NATIVE>(div_by_recip(x, s, r));
+                t = rnd<T, NATIVE>(__fadd_rn(t, zf));
+                t = fminf(fmaxf(t, 0.0f), QMAX);
+                const uint32_t mul = 1u << ((pos0 + i) * BITS);
+                acc += __float_as_uint(__fadd_rn(t, MAGIC)) * mul;
+                bias += MAGIC_BITS * mul;
+            }
+            words[wi] = acc - bias;
+        }
+    } else {
+        // step-by-step path with torch's NaN propagation (amin/amax keep NaN)
+        float mn2 = v[0], mx2 = v[0];
+#pragma unroll
+        for (int j = 1; j < V; ++j) { mn2 = min_nanprop(mn2, v[j]); mx2 = max_nanprop(mx2, v[j]); }
+        for (int off = cpg >> 1; off > 0; off >>= 1) {
+            // only lanes of this group's segment hold meaningful values; the shuffle is
+            // executed by the lanes that took this branch
+            mn2 = min_nanprop(mn2, __shfl_xor_sync(__activemask(), mn2, off));
+            mx2 = max_nanprop(mx2, __shfl_xor_sync(__activemask(), mx2, off));
+        }
+        group_params<T, NATIVE>(mn2, mx2, QMAX, floor_s, s, zi, zf);
+        const int pos0 = (V >= VPI) ? 0 : (lane & (VPI / V - 1)) * V;
+#pragma unroll
+        for (int wi = 0; wi < (V >= VPI ? V / VPI : 1); ++wi) {
+            uint32_t acc = 0;
+#pragma unroll
+            for (int i = 0; i < (V >= VPI ? VPI : V); ++i)
+                acc |= code_of<T, NATIVE>(v[wi * VPI + i], s, zf, QMAX) << ((pos0 + i) * BITS);
+            words[wi] = acc;
+        }
+    }
+    if (in_range && (lane & (cpg - 1)) == 0) {
+        const int64_t gidx = c >> cpg_log2;
+        scale[gidx] = from_f32<ST>(s);
+        store_zp<ZT>(zp + gidx, zi);
+    }
+    if constexpr (V >= VPI) {
+        constexpr int WPC = V / VPI;     // this thread owns V/VPI whole words
+        if (in_range) {
+            if constexpr (WPC == 1) qweight[c] = (int32_t)words[0];
+            else if constexpr (WPC == 2)
+                *reinterpret_cast<uint2 *>(qweight + c * 2) = make_uint2(words[0], words[1]);
+            else {
+#pragma unroll
+                for (int wi = 0; wi < WPC; ++wi) qweight[c * WPC + wi] = (int32_t)words[wi];
+            }
+        }
+    } else {
+        constexpr int LPW = VPI / V;     // VPI/V consecutive lanes hold the codes of one word
+        uint32_t acc = words[0];
+#pragma unroll
+        for (int off = 1; off < LPW; off <<= 1) acc |= __shfl_xor_sync(0xffffffffu, acc, off);
+        if (in_range && (lane & (LPW - 1)) == 0) qweight[c / LPW] = (int32_t)acc;
+    }
+}
+
 template <typename T, bool NATIVE, int BITS, int L, typename ST, typename ZT>
 __global__ void __launch_bounds__(256)
 rtn_quantize_pack_kernel(const T *__restrict__ w, int64_t total_chunks, int cpg_log2, float floor_s,
                          int32_t *__restrict__ qweight, ST *__restrict__ scale, ZT *__restrict__ zp) {
     constexpr int V = Elems16<T>::V;
-    constexpr int VPI = 32 / BITS;
-    constexpr float QMAX = (float)((1 << BITS) - 1);
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t c0 = warp * (32 * L) + lane;
     const int cpg = 1 << cpg_log2;
-
+    const uint32_t seg_mask = (cpg == 32) ? 0xffffffffu : (((1u << cpg) - 1u) << (lane & ~(cpg - 1)));
     float v[L][V];
 #pragma unroll
     for (int l = 0; l < L; ++l) {
@@ -117,52 +267,106 @@ rtn_quantize_pack_kernel(const T *__restrict__ w, int64_t total_chunks, int cpg_
 #pragma unroll
     for (int l = 0; l < L; ++l) {
         const int64_t c = c0 + l * 32;
-        float mn = v[l][0], mx = v[l][0];
-#pragma unroll
-        for (int j = 1; j < V; ++j) { mn = min_nanprop(mn, v[l][j]); mx = max_nanprop(mx, v[l][j]); }
-        for (int off = cpg >> 1; off > 0; off >>= 1) {
-            mn = min_nanprop(mn, __shfl_xor_sync(0xffffffffu, mn, off));
-            mx = max_nanprop(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        rtn_slot<T, NATIVE, BITS, ST, ZT>(v[l], c, c < total_chunks, lane, cpg, cpg_log2, seg_mask, floor_s,
+                                          qweight, scale, zp);
+    }
+}
+
+// ---- streaming variant of the fast path: bulk-async copies into a shared-memory ring ------
+//
+// HBM latency under load on B200 is about 2 us, so ~100 KB per SM have to be in flight to
+// approach the bandwidth roofline -- more than register-resident loads of a compute-heavy
+// kernel can hold.  Persistent CTAs therefore pull the (fully contiguous) weight stream with
+// cp.async.bulk (the 1-D form of the TMA engine) into a STAGES-deep ring of 16 KB tiles,
+// completion signalled on mbarriers; all threads then read their 16-byte chunks from
+// shared memory (lane-contiguous, conflict-free) and run the same per-chunk code as above.
+// Every wait is bounded: a wait that runs out sets g_rtn_status and the thread returns.
+__device__ int g_rtn_status = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, unsigned bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+constexpr int RTN_STAGES = 4;
+constexpr int RTN_THREADS = 512;
+constexpr int RTN_L = 2;                                   // 16-byte chunks per thread per tile
+constexpr int RTN_TILE_CHUNKS = RTN_THREADS * RTN_L;       // 16 KB tiles
+constexpr unsigned RTN_WAIT_LIMIT = 1u << 22;
+
+template <typename T, bool NATIVE, int BITS, typename ST, typename ZT>
+__global__ void __launch_bounds__(RTN_THREADS, 3)
+rtn_quantize_pack_stream_kernel(const T *__restrict__ w, int64_t total_chunks, int64_t num_tiles, int cpg_log2,
+                                float floor_s, int32_t *__restrict__ qweight, ST *__restrict__ scale,
+                                ZT *__restrict__ zp) {
+    constexpr int V = Elems16<T>::V;
+    extern __shared__ __align__(128) unsigned char rtn_smem[];
+    uint4 *ring = reinterpret_cast<uint4 *>(rtn_smem);                         // [STAGES][TILE_CHUNKS]
+    uint64_t *full = reinterpret_cast<uint64_t *>(ring + RTN_STAGES * RTN_TILE_CHUNKS);
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int cpg = 1 << cpg_log2;
+    const uint32_t seg_mask = (cpg == 32) ? 0xffffffffu : (((1u << cpg) - 1u) << (lane & ~(cpg - 1)));
+    const uint4 *src = reinterpret_cast<const uint4 *>(w);
+
+    auto tile_of = [&](int64_t it) { return (int64_t)blockIdx.x + it * gridDim.x; };
+    auto issue = [&](int64_t it) {                          // thread 0 only
+        const int64_t tile = tile_of(it);
+        if (tile >= num_tiles) return;
+        const int st = (int)(it % RTN_STAGES);
+        const int64_t first = tile * RTN_TILE_CHUNKS;
+        const int64_t n = (total_chunks - first < RTN_TILE_CHUNKS) ? (total_chunks - first) : RTN_TILE_CHUNKS;
+        mbar_expect_tx(&full[st], (unsigned)(n * 16));
+        bulk_g2s(ring + st * RTN_TILE_CHUNKS, src + first, (unsigned)(n * 16), &full[st]);
+    };
+    if (tid == 0) {
+        for (int s = 0; s < RTN_STAGES; ++s) mbar_init(&full[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (int s = 0; s < RTN_STAGES; ++s) issue(s);
+    }
+    for (int64_t it = 0; tile_of(it) < num_tiles; ++it) {
+        const int st = (int)(it % RTN_STAGES);
+        const unsigned parity = (unsigned)((it / RTN_STAGES) & 1);
+        unsigned tries = 0;
+        while (!mbar_try_wait(&full[st], parity)) {
+            if (++tries > RTN_WAIT_LIMIT) { atomicExch(&g_rtn_status, 1); return; }
         }
-        float s, zf; int32_t zi;
-        group_params<T, NATIVE>(mn, mx, QMAX, floor_s, s, zi, zf);
-        if (c < total_chunks && (lane & (cpg - 1)) == 0) {
-            const int64_t gidx = c >> cpg_log2;
-            scale[gidx] = from_f32<ST>(s);
-            store_zp<ZT>(zp + gidx, zi);
+        const int64_t first = tile_of(it) * RTN_TILE_CHUNKS;
+        const uint4 *tile = ring + st * RTN_TILE_CHUNKS;
+        float v[RTN_L][V];
+#pragma unroll
+        for (int l = 0; l < RTN_L; ++l) {
+            const int cl = (tid >> 5) * (32 * RTN_L) + l * 32 + lane;
+            if (first + cl < total_chunks) unpack16<T>(tile[cl], v[l]);
+            else {
+#pragma unroll
+                for (int j = 0; j < V; ++j) v[l][j] = 0.0f;
+            }
         }
-        if constexpr (V >= VPI) {
-            // this thread owns V/VPI whole words
-            constexpr int WPC = V / VPI;
-            uint32_t words[WPC];
+        __syncthreads();                                    // the whole CTA has read this stage
+        if (tid == 0) issue(it + RTN_STAGES);
 #pragma unroll
-            for (int wi = 0; wi < WPC; ++wi) {
-                uint32_t acc = 0;
-#pragma unroll
-                for (int i = 0; i < VPI; ++i)
-                    acc |= code_of<T, NATIVE>(v[l][wi * VPI + i], s, zf, QMAX) << (i * BITS);
-                words[wi] = acc;
-            }
-            if (c < total_chunks) {
-                if constexpr (WPC == 1) qweight[c] = (int32_t)words[0];
-                else if constexpr (WPC == 2)
-                    *reinterpret_cast<uint2 *>(qweight + c * 2) = make_uint2(words[0], words[1]);
-                else {
-#pragma unroll
-                    for (int wi = 0; wi < WPC; ++wi) qweight[c * WPC + wi] = (int32_t)words[wi];
-                }
-            }
-        } else {
-            // VPI/V consecutive lanes hold the codes of one word
-            constexpr int LPW = VPI / V;
-            const int pos0 = (lane & (LPW - 1)) * V;
-            uint32_t acc = 0;
-#pragma unroll
-            for (int j = 0; j < V; ++j)
-                acc |= code_of<T, NATIVE>(v[l][j], s, zf, QMAX) << ((pos0 + j) * BITS);
-#pragma unroll
-            for (int off = 1; off < LPW; off <<= 1) acc |= __shfl_xor_sync(0xffffffffu, acc, off);
-            if (c < total_chunks && (lane & (LPW - 1)) == 0) qweight[c / LPW] = (int32_t)acc;
+        for (int l = 0; l < RTN_L; ++l) {
+            const int64_t c = first + (tid >> 5) * (32 * RTN_L) + l * 32 + lane;
+            rtn_slot<T, NATIVE, BITS, ST, ZT>(v[l], c, c < total_chunks, lane, cpg, cpg_log2, seg_mask, floor_s,
+                                              qweight, scale, zp);
         }
     }
 }
@@ -223,6 +427,10 @@ rtn_quantize_pack_general_kernel(const T *__restrict__ w, int64_t num_spans, int
     }
 }
 
+// The bulk-async variant is correct and tested but currently slower than the register-load
+// kernel (both are instruction-issue bound, about 30 instructions per weight), so it is opt-in.
+bool g_rtn_stream = false;
+
 int64_t gcd64(int64_t a, int64_t b) { while (b) { int64_t t = a % b; a = b; b = t; } return a; }
 
 template <typename T, bool NATIVE, int BITS, typename ST, typename ZT>
@@ -243,6 +451,15 @@ int launch_typed(const T *w, int64_t N, int64_t K, int g, int32_t *q, ST *scale,
         const int64_t warps = (chunks + 32 * L - 1) / (32 * L);
         const int64_t blocks = (warps + 7) / 8;
         if (blocks > 0x7fffffff) return BW_ERR_SHAPE;
+        const int64_t tiles = (chunks + RTN_TILE_CHUNKS - 1) / RTN_TILE_CHUNKS;
+        if (g_rtn_stream && tiles >= 148 * 4) {
+            auto kern = rtn_quantize_pack_stream_kernel<T, NATIVE, BITS, ST, ZT>;
+            const size_t smem = (size_t)RTN_STAGES * RTN_TILE_CHUNKS * 16 + RTN_STAGES * sizeof(uint64_t);
+            BW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            const int64_t grid = tiles < 148 * 3 ? tiles : 148 * 3;
+            kern<<<(unsigned)grid, RTN_THREADS, smem, st>>>(w, chunks, tiles, cpg_log2, floor_s, q, scale, zp);
+            return check_launch("rtn_quantize_pack_stream_kernel");
+        }
         rtn_quantize_pack_kernel<T, NATIVE, BITS, L, ST, ZT><<<(unsigned)blocks, 256, 0, st>>>(
             w, chunks, cpg_log2, floor_s, q, scale, zp);
         return check_launch("rtn_quantize_pack_kernel");
@@ -286,6 +503,49 @@ int launch_scale(const T *w, int64_t N, int64_t K, int bits, int g, int32_t *q, 
 }
 
 }  // namespace
+
+// Test hook: compares div_by_recip with __fdiv_rn on pseudo-random operand pairs inside the
+// fast path's domain (plus adversarial significands); returns the number of mismatches.
+__global__ void div_check_kernel(uint64_t n, uint64_t seed, unsigned long long *mismatches) {
+    unsigned long long bad = 0;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t z = (i + 1) * 0x9E3779B97F4A7C15ull + seed;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull; z = (z ^ (z >> 27)) * 0x94D049BB133111EBull; z ^= z >> 31;
+        uint32_t mv = (uint32_t)z & 0x7fffffu, ms = (uint32_t)(z >> 23) & 0x7fffffu;
+        const uint32_t kind = (uint32_t)(z >> 60);
+        if (kind == 0) ms = 0x7fffffu;                 // all-ones divisor significand
+        else if (kind == 1) ms = 0;                    // power of two
+        else if (kind == 2) ms = 0x7ffffeu;
+        else if (kind == 3) mv = 0x7fffffu;
+        else if (kind == 4) mv = ms;                   // quotient exactly 1 * 2^k
+        else if (kind == 5) ms &= 0x7ff000u;           // short divisor significands (fp16/bf16 scales)
+        const int ev = 127 - 38 + (int)((z >> 46) % 77);   // |v| in [2^-38, 2^38]
+        const int es = 127 - 39 + (int)((z >> 53) % 78);   // s in [2^-39, 2^38]
+        const float v = __uint_as_float(((uint32_t)(z >> 45) & 1u) << 31 | (uint32_t)ev << 23 | mv);
+        const float s = __uint_as_float((uint32_t)es << 23 | ms);
+        const float a = div_by_recip(v, s, __frcp_rn(s)), b = __fdiv_rn(v, s);
+        if (__float_as_uint(a) != __float_as_uint(b)) ++bad;
+    }
+    if (bad) atomicAdd(mismatches, bad);
+}
+long long div_self_check(unsigned long long n, unsigned long long seed) {
+    unsigned long long *d = nullptr, h = 0;
+    if (cudaMalloc(&d, sizeof(h)) != cudaSuccess) return -1;
+    cudaMemset(d, 0, sizeof(h));
+    div_check_kernel<<<148 * 8, 256>>>(n, seed, d);
+    const cudaError_t e = cudaMemcpy(&h, d, sizeof(h), cudaMemcpyDeviceToHost);
+    cudaFree(d);
+    return e == cudaSuccess ? (long long)h : -1;
+}
+
+// Reads and clears the status word the bounded waits set (0 = no wait ever ran out).
+int rtn_device_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_rtn_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v) (void)cudaMemcpyToSymbol(g_rtn_status, &zero, sizeof(int));
+    return v;
+}
+void set_rtn_stream(int on) { g_rtn_stream = on != 0; }
 
 int rtn_quantize_pack(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int g,
                       int32_t *q, void *scale, int scale_dtype, void *zp, int zp_dtype,

@@ -63,6 +63,12 @@ def _declare(L):
     L.bw_version.restype = i32
     L.bw_debug_set_smallm_tuning.argtypes = [i32, i32, i32]
     L.bw_debug_set_smallm_tuning.restype = None
+    L.bw_device_status.argtypes = []
+    L.bw_device_status.restype = i32
+    L.bw_debug_set_rtn_stream.argtypes = [i32]
+    L.bw_debug_set_rtn_stream.restype = None
+    L.bw_debug_div_self_check.argtypes = [ctypes.c_ulonglong, ctypes.c_ulonglong]
+    L.bw_debug_div_self_check.restype = ctypes.c_longlong
     L.bw_debug_set_pdl.argtypes = [i32]
     L.bw_debug_set_pdl.restype = None
 

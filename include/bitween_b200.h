@@ -146,6 +146,9 @@ BW_API int bw_qmatmul_grad_input(const void *grad_out, int grad_dtype, int64_t M
 BW_API const char *bw_status_string(int status);
 /* Text of the last CUDA error seen by this thread inside the library ("" if none). */
 BW_API const char *bw_last_cuda_error(void);
+/* Synchronizes the current device and reports whether any bounded device-side wait of the
+ * library's kernels ran out since the last call (BW_ERR_TIMEOUT), clearing the flag. */
+BW_API int bw_device_status(void);
 /* Library version: major*10000 + minor*100 + patch. */
 BW_API int bw_version(void);
 /* Name of the kernel the last bw_qmatmul call of this thread dispatched to (diagnostics). */

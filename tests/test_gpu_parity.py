@@ -125,6 +125,41 @@ def test_rtn_upcast_mode_equals_fp32_path():
     assert _bits_equal(z_h, oracle.f16_bits(zo.astype(np.float32)))
 
 
+def test_rtn_division_by_reciprocal_is_correctly_rounded():
+    # the RTN kernel divides by one correctly rounded reciprocal per group plus four FMAs per
+    # element; on 2^28 operand pairs (random and adversarial significands, the whole exponent
+    # range of the fast path) the result must equal IEEE division bit for bit
+    L = _lib.lib()
+    for seed in (1, 2):
+        assert L.bw_debug_div_self_check(1 << 27, seed) == 0
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_rtn_streaming_kernel_equals_register_kernel(dt):
+    # the opt-in bulk-async (TMA 1-D) pipeline must give the same bits as the default
+    # register-load kernel, ragged last tile included, and no bounded wait may run out
+    L = _lib.lib()
+    N, K = 2051, 4096                      # not a multiple of the 16 KB tile
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    w = (torch.randn(N, K, device=DEV, generator=gen) * 0.02).to(TORCH_DT[dt])
+    w[7, 128:256] = 0.25                   # a constant group
+    if dt == "f32":
+        w[11, 5] = float("inf")            # sends one group down the NaN/Inf-propagating path
+    for bits, g in ((4, 128), (8, 32), (2, 64)):
+        ref = quantize_rtn(w, bits=bits, group_size=g)
+        try:
+            L.bw_debug_set_rtn_stream(1)
+            got = quantize_rtn(w, bits=bits, group_size=g)
+        finally:
+            L.bw_debug_set_rtn_stream(0)
+        assert L.bw_device_status() == 0
+        for a, b in zip(got[:3], ref[:3]):
+            assert _bits_equal(a, to_np(b)), (dt, bits, g)
+    # and the oracle agrees on a slice (rows are independent)
+    qo, so, zo = oracle.quantize_rtn(to_np(w[:16].cpu()), ORACLE_DT[w.dtype], 2, 64)
+    assert _bits_equal(got[0][:16], qo) and _bits_equal(got[1][:16], so) and _bits_equal(got[2][:16], zo)
+
+
 def test_rtn_error_bound_full_size_layer():
     # size-independent property at a full Llama-3-8B shape: |w - dequant| <= scale/2 per element
     torch.manual_seed(0)
