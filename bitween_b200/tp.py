@@ -1,0 +1,138 @@
+"""Tensor-parallel sharding of QuantizedLinear layers over the GPUs of one node, and
+layer-wise sharding of RTN quantization.
+
+The reference has no distributed code at all; this module adds the Megatron-style split that
+the packed layout allows without re-quantizing:
+
+  column-parallel (q/k/v, gate/up): split out_features -> contiguous ROW blocks of
+      qweight [N/tp, K*bits/32], scale / zero_point [N/tp, K/g], bias [N/tp]; the input is
+      replicated and the output stays sharded (it feeds the next row-parallel layer).
+  row-parallel (o_proj, down_proj): split in_features -> COLUMN blocks qweight[:, (K/tp)*bits/32],
+      scale / zero_point[:, (K/tp)/g]; needs (K/tp) % group_size == 0 and (K/tp) % (32/bits) == 0
+      so that no group and no packed word straddles two ranks; each rank produces a partial
+      [M, N] that one all-reduce (NCCL over NVLink / NVSwitch) sums.  The bias is added on
+      rank 0 only, i.e. exactly once.
+
+Groups never straddle a shard, so quantize-then-shard equals shard-then-quantize bit for bit.
+One process per GPU; `torch.distributed` (backend "nccl") is the plumbing.
+"""
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .kernels.cuda_loader import quantized_matmul_cuda
+from .modules import QuantizedLinear
+
+
+def _matmul(*args, **kwargs):
+    """Indirection point: the GPU kernel call (tests on CPU ranks substitute a checker here)."""
+    return quantized_matmul_cuda(*args, **kwargs)
+
+
+def check_row_parallel(in_features, bits, group_size, world):
+    """Raises ValueError unless in_features splits over `world` ranks on group and word boundaries."""
+    if in_features % world != 0:
+        raise ValueError(f"in_features={in_features} is not divisible by tensor-parallel size {world}")
+    k = in_features // world
+    if k % group_size != 0:
+        raise ValueError(f"row-parallel shard of {k} input features is not a multiple of group_size={group_size}")
+    if k % (32 // bits) != 0:
+        raise ValueError(f"row-parallel shard of {k} input features is not a multiple of {32 // bits} codes per word")
+    return k
+
+
+def shard_quantized_linear(layer: QuantizedLinear, mode: str, rank: int, world: int) -> QuantizedLinear:
+    """Returns the rank's shard of `layer` as a new QuantizedLinear (buffers are copies)."""
+    if mode not in ("column", "row"):
+        raise ValueError("mode must be 'column' or 'row'")
+    if not 0 <= rank < world:
+        raise ValueError("rank out of range")
+    N, K, bits, g = layer.out_features, layer.in_features, layer.bits, layer.group_size
+    vpi = 32 // bits
+    if mode == "column":
+        if N % world != 0:
+            raise ValueError(f"out_features={N} is not divisible by tensor-parallel size {world}")
+        n = N // world
+        out = QuantizedLinear(K, n, bits, g, bias=layer.bias is not None)
+        rows = slice(rank * n, (rank + 1) * n)
+        out.qweight = layer.qweight[rows].contiguous()
+        out.scale = layer.scale[rows].contiguous()
+        out.zero_point = layer.zero_point[rows].contiguous()
+        if layer.bias is not None:
+            out.bias = layer.bias[rows].contiguous()
+        return out
+    k = check_row_parallel(K, bits, g, world)
+    out = QuantizedLinear(k, N, bits, g, bias=layer.bias is not None and rank == 0)
+    out.qweight = layer.qweight[:, rank * (k // vpi):(rank + 1) * (k // vpi)].contiguous()
+    out.scale = layer.scale[:, rank * (k // g):(rank + 1) * (k // g)].contiguous()
+    out.zero_point = layer.zero_point[:, rank * (k // g):(rank + 1) * (k // g)].contiguous()
+    if layer.bias is not None and rank == 0:
+        out.bias = layer.bias.clone()
+    return out
+
+
+class ColumnParallelQuantizedLinear(nn.Module):
+    """Holds rows [rank*N/tp, (rank+1)*N/tp) of a QuantizedLinear; no communication.
+    `gather_output=True` all-gathers the sharded outputs along the last dimension."""
+
+    def __init__(self, shard: QuantizedLinear, group=None, gather_output=False):
+        super().__init__()
+        self.shard = shard
+        self.group = group
+        self.gather_output = gather_output
+
+    @classmethod
+    def from_full(cls, layer, rank, world, group=None, gather_output=False):
+        return cls(shard_quantized_linear(layer, "column", rank, world), group, gather_output)
+
+    def forward(self, x):
+        s = self.shard
+        y = _matmul(x, s.qweight, s.scale, s.zero_point, s.bias, s.bits, s.group_size)
+        if self.gather_output and dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            parts = [torch.empty_like(y) for _ in range(dist.get_world_size(self.group))]
+            dist.all_gather(parts, y.contiguous(), group=self.group)
+            y = torch.cat(parts, dim=-1)
+        return y
+
+
+class RowParallelQuantizedLinear(nn.Module):
+    """Holds input columns [rank*K/tp, (rank+1)*K/tp) of a QuantizedLinear; the input is the
+    matching slice of the activations and the partial outputs are summed with one all-reduce."""
+
+    def __init__(self, shard: QuantizedLinear, group=None):
+        super().__init__()
+        self.shard = shard
+        self.group = group
+
+    @classmethod
+    def from_full(cls, layer, rank, world, group=None):
+        return cls(shard_quantized_linear(layer, "row", rank, world), group)
+
+    def forward(self, x_shard):
+        s = self.shard
+        if x_shard.shape[-1] != s.in_features:
+            raise ValueError(f"row-parallel input has {x_shard.shape[-1]} features, this rank holds {s.in_features}")
+        y = _matmul(x_shard, s.qweight, s.scale, s.zero_point, s.bias, s.bits, s.group_size)
+        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+        return y
+
+
+def layer_shard_filter(rank: int, world: int):
+    """`layer_filter` for Bitween.quantize: rank r quantizes layers r, r+world, ... (layers are
+    independent, so RTN quantization shards over GPUs with no communication)."""
+    if not 0 <= rank < world:
+        raise ValueError("rank out of range")
+    return lambda index, name: index % world == rank
+
+
+def check_same_across_ranks(values, group=None):
+    """Host-side consistency check before a collective: every rank must agree on `values`
+    (a tuple of ints, e.g. shapes).  Raises RuntimeError on the ranks that differ from rank 0."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return
+    mine = [int(v) for v in values]
+    gathered = [None] * dist.get_world_size(group)
+    dist.all_gather_object(gathered, mine, group=group)
+    if any(g != gathered[0] for g in gathered):
+        raise RuntimeError(f"tensor-parallel ranks disagree: {gathered}")
