@@ -77,7 +77,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -333,7 +333,7 @@ def run_extras(args, torch, fn, qmm, device, gen):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto")
@@ -396,15 +396,15 @@ def main():
                              "algorithmic_bytes_per_launch": res["bytes_per_launch"]},
                 "breakdown": res.get("breakdown", {}), "extra": res.get("extra", {})}
         if world == 1 and not args.no_cpu:
-            sample = [LLAMA8B_SHAPES[1], LLAMA8B_SHAPES[0]]
             from oracle import oracle
             oracle.build()
-            cpu_decode_sample(sample[:1], [1])
-            b, s = cpu_decode_sample(sample, DECODE_M, repeats=2)
+            cpu_decode_sample(LLAMA8B_SHAPES[1:2], [1])
+            b, s = cpu_decode_sample(LLAMA8B_SHAPES, DECODE_M, repeats=4)
             line["cpu_baseline"] = {
                 "value": b / s / 1e9, "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
-                "sample": "M in {1,2,4,8,16} x {4096->1024, 4096->4096} W4 g128, 2 repeats "
-                          f"({s:.1f} s of CPU time), oracle port of the reference's CPU dequantize+matmul"}
+                "sample": "the whole decode sweep (M in {1,2,4,8,16} x the four Llama-3-8B shapes, W4 g128), "
+                          f"4 repeats, one layer copy ({s:.1f} s of CPU time); oracle port of the reference's "
+                          "CPU dequantize + matmul, OpenMP over all host threads"}
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
