@@ -31,6 +31,7 @@ bool smallm_fast_path_ok(const void *x, int x_dtype, int64_t K, const int32_t *q
 size_t smallm_workspace_bytes(int64_t M, int64_t K, int bits);
 void set_smallm_tuning(int rt, int warps, int splits);
 void set_smallm_pdl(int on);
+int noalloc_scratch(void **ptr, size_t *bytes);
 int rtn_device_status();
 void set_rtn_stream(int on);
 long long div_self_check(unsigned long long n, unsigned long long seed);
@@ -123,6 +124,30 @@ int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
     return BW_OK;
 }
 
+int bw_qmatmul_noalloc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K,
+                       const int32_t *qweight, const void *scale, const void *zero_point,
+                       const void *bias, void *out, int out_dtype, int bits, int group_size,
+                       void *stream) {
+    int rc = check_quant_shape(N, K, bits, group_size);
+    if (rc != BW_OK) return rc;
+    if (M < 0) return BW_ERR_SHAPE;
+    // reject requests whose prepared activations do not fit the built-in scratch before
+    // anything is launched
+    void *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    rc = noalloc_scratch(&scratch, &scratch_bytes);
+    if (rc != BW_OK) return rc;
+    if (bw_qmatmul_workspace_bytes(M, N, K, bits, group_size) > scratch_bytes) return BW_ERR_TOO_LARGE;
+    return bw_qmatmul(x, x_dtype, M, N, K, qweight, scale, zero_point, bias, out, out_dtype, bits,
+                      group_size, scratch, scratch_bytes, stream);
+}
+
+size_t bw_qmatmul_noalloc_max_scratch_bytes(void) {
+    void *p = nullptr;
+    size_t b = 0;
+    return noalloc_scratch(&p, &b) == BW_OK ? b : 0;
+}
+
 int bw_qmatmul_host(const void *x_host, int x_dtype, int64_t M, int64_t N, int64_t K,
                     const int32_t *qweight, const void *scale, const void *zero_point,
                     const void *bias, void *out_host, int out_dtype, int bits, int group_size,
@@ -175,6 +200,9 @@ const char *bw_status_string(int status) {
         case BW_ERR_CUDA: return "CUDA runtime error (see bw_last_cuda_error)";
         case BW_ERR_UNSUPPORTED: return "no kernel for this request";
         case BW_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+        case BW_ERR_TOO_LARGE:
+            return "request needs more scratch than the 2 MiB built into bw_qmatmul_noalloc "
+                   "(K rounded up to a k-chunk x 8*ceil(min(M,64)/8) x 2 bytes); use bw_qmatmul with a workspace";
         default: return "unknown status";
     }
 }

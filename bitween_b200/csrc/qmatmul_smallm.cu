@@ -704,6 +704,33 @@ bool smallm_fast_path_ok(const void *x, int x_dtype, int64_t K, const int32_t *q
     return true;
 }
 
+// ---- built-in scratch for bw_qmatmul_noalloc ------------------------------------------------
+// Some callers may not allocate device memory at all: code running while a CUDA graph is being
+// captured, real-time serving loops that forbid allocator calls after start-up, and plugins
+// whose host hands them only input/output buffers.  For them the prepared-activation scratch
+// lives in this fixed array instead of a caller-supplied workspace.  Every GPU that loads the
+// library reserves these 2 MiB until the process exits.  All calls on a device share the
+// array, so calls that overlap on the GPU (different streams) would race on it.
+constexpr size_t NOALLOC_SCRATCH_BYTES = (size_t)2 << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+// Device address of the built-in scratch on the CURRENT device.  In host code the array's
+// name is only a handle for the runtime, not a device pointer, so the address is looked up
+// with cudaGetSymbolAddress -- once per device, with that device current -- and cached.
+int noalloc_scratch(void **ptr, size_t *bytes) {
+    static void *cached[64] = {};
+    int dev = 0;
+    BW_CUDA_TRY(cudaGetDevice(&dev));
+    void *p = (dev >= 0 && dev < 64) ? cached[dev] : nullptr;
+    if (!p) {
+        BW_CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        if (dev >= 0 && dev < 64) cached[dev] = p;   // racing first calls store the same value
+    }
+    *ptr = p;
+    *bytes = NOALLOC_SCRATCH_BYTES;
+    return BW_OK;
+}
+
 // Scratch bytes the streaming kernel needs for the prepared activations of one launch.
 size_t smallm_workspace_bytes(int64_t M, int64_t K, int bits) {
     const int kc = 16 * (32 / bits);

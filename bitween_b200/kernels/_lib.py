@@ -48,6 +48,10 @@ def _declare(L):
     L.bw_qmatmul_workspace_bytes.restype = sz
     L.bw_qmatmul.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, vp, vp, i32, i32, i32, vp, sz, vp]
     L.bw_qmatmul.restype = i32
+    L.bw_qmatmul_noalloc.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, vp, vp, i32, i32, i32, vp]
+    L.bw_qmatmul_noalloc.restype = i32
+    L.bw_qmatmul_noalloc_max_scratch_bytes.argtypes = []
+    L.bw_qmatmul_noalloc_max_scratch_bytes.restype = sz
     L.bw_qmatmul_host.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp,
                                   sz, vp]
     L.bw_qmatmul_host.restype = i32

@@ -134,3 +134,38 @@ def quantized_matmul_host(x_host, qweight, scale, zero_point, bias, bits, group_
                                _lib.stream_ptr(dev))
     _lib.check(rc)
     return out_host
+
+
+def quantized_matmul_noalloc(x, qweight, scale, zero_point, bias, bits, group_size, out):
+    """Fused dequantize+matmul for callers that must not allocate device memory (inside a CUDA
+    graph capture, in an allocation-free serving loop, in a plugin that only receives buffers).
+
+    Same result as `quantized_matmul_cuda`, but nothing is allocated here or in the library: the
+    caller passes the output tensor, every tensor must already be a contiguous CUDA tensor of
+    its final dtype (fp16 scale / zero_point / bias), and the kernel's scratch is a fixed 2 MiB
+    array inside the library (C ABI: bw_qmatmul_noalloc).  Requests that need more scratch raise
+    BitweenKernelError (status 11).  All calls on one device share that array: issue them on
+    one stream.  Make the first call on a device outside stream capture."""
+    for name, t in (("x", x), ("qweight", qweight), ("scale", scale), ("zero_point", zero_point), ("out", out)):
+        _lib.require_cuda(t, name)
+        if not t.is_contiguous():
+            raise ValueError(f"`{name}` must be contiguous (this call may not make copies)")
+    if bias is not None and (not bias.is_cuda or not bias.is_contiguous() or bias.dtype != torch.float16):
+        raise ValueError("`bias` must be a contiguous fp16 CUDA tensor")
+    if scale.dtype != torch.float16 or zero_point.dtype != torch.float16 or qweight.dtype != torch.int32:
+        raise TypeError("qweight must be int32 and scale / zero_point fp16")
+    if x.dtype not in _OUT_DTYPES or out.dtype not in _OUT_DTYPES:
+        raise TypeError("x / out must be fp16, bf16 or fp32")
+    K = x.shape[-1]
+    N = qweight.shape[0]
+    M = x.numel() // K if K else 0
+    if qweight.shape[1] * (32 // bits) != K or out.numel() != M * N:
+        raise ValueError("shape mismatch between x, qweight and out")
+    dev = x.device
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        rc = L.bw_qmatmul_noalloc(_lib.ptr(x), _lib.dtype_code(x.dtype), M, N, K, _lib.ptr(qweight),
+                                  _lib.ptr(scale), _lib.ptr(zero_point), _lib.ptr(bias), _lib.ptr(out),
+                                  _lib.dtype_code(out.dtype), bits, group_size, _lib.stream_ptr(dev))
+    _lib.check(rc)
+    return out

@@ -51,7 +51,8 @@ typedef enum {
     BW_ERR_WORKSPACE = 7,   /* workspace smaller than bw_qmatmul_workspace_bytes()             */
     BW_ERR_CUDA = 8,        /* a CUDA runtime call failed; see bw_last_cuda_error()            */
     BW_ERR_UNSUPPORTED = 9, /* valid request this build has no kernel for                      */
-    BW_ERR_TIMEOUT = 10     /* a bounded device-side wait ran out (reported via status word)   */
+    BW_ERR_TIMEOUT = 10,    /* a bounded device-side wait ran out (reported via status word)   */
+    BW_ERR_TOO_LARGE = 11   /* request exceeds the fixed scratch of bw_qmatmul_noalloc         */
 } bw_status;
 
 /* flags for bw_rtn_quantize_pack */
@@ -119,6 +120,34 @@ BW_API int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t 
                const int32_t *qweight, const void *scale, const void *zero_point,
                const void *bias, void *out, int out_dtype, int bits, int group_size,
                void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * bw_qmatmul for callers that cannot allocate device memory.  (No counterpart in the
+ * reference: its forward allocates a temporary fp16 [N,K] on every call.)
+ *
+ * Who needs it: code that runs while a CUDA graph is being captured or inside a latency-bound
+ * serving loop where allocator calls are forbidden after start-up, and host plugins that are
+ * handed only their input and output buffers.  Instead of a caller-supplied workspace the
+ * prepared activations go to a 2 MiB array that is part of the library image (every GPU that
+ * loads the library holds it until the process exits).  The call makes no cudaMalloc /
+ * cudaFree and uses no allocating library routine; the caller still owns x, the packed
+ * weights and out.
+ *
+ * Limit: K (rounded up to a k-chunk of 16*32/bits) * 8*ceil(min(M,64)/8) * 2 bytes must not
+ * exceed bw_qmatmul_noalloc_max_scratch_bytes() (2 MiB: e.g. K <= 65536 for M <= 16,
+ * K <= 16384 for M >= 57); otherwise BW_ERR_TOO_LARGE is returned and nothing is launched.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
+ * that device current) -- make that first call before starting a stream capture.
+ * All calls on a device share the array and it keeps the last call's contents; every call
+ * rewrites the part it reads (padding included), so nothing has to be cleared, but calls that
+ * overlap on the GPU (different streams) race on it -- issue them on one stream.
+ * Arguments and results are exactly those of bw_qmatmul.
+ */
+BW_API int bw_qmatmul_noalloc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K,
+                       const int32_t *qweight, const void *scale, const void *zero_point,
+                       const void *bias, void *out, int out_dtype, int bits, int group_size,
+                       void *stream);
+BW_API size_t bw_qmatmul_noalloc_max_scratch_bytes(void);
 
 /*
  * Same operator with HOST activations and HOST output (pinned memory for true overlap):
