@@ -81,6 +81,10 @@ class ClockSampler:
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
+            t0 = time.time()
+            while not self.lines and time.time() - t0 < 3.0:   # nvidia-smi needs a moment to start
+                time.sleep(0.02)
+            self.lines.clear()                                  # keep only samples taken under load
         except OSError:
             self.proc = None
 
@@ -89,6 +93,7 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def stop(self):
+        time.sleep(0.05)
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()

@@ -32,11 +32,21 @@ size_t smallm_workspace_bytes(int64_t M, int64_t K, int bits);
 void set_smallm_tuning(int rt, int warps, int splits);
 void set_smallm_pdl(int on);
 int noalloc_scratch(void **ptr, size_t *bytes);
+bool tc_path_ok(int64_t M, int64_t N, int64_t K, const int32_t *q, int bits, int g);
+size_t tc_workspace_bytes(int64_t M, int64_t K);
+int tc_device_status();
+void set_tc_enabled(int on);
+int qmatmul_tc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
+               const __half *scale, const __half *zp, const __half *bias, void *out, int out_dtype, int bits,
+               int g, void *workspace, cudaStream_t st);
 int rtn_device_status();
 void set_rtn_stream(int on);
 long long div_self_check(unsigned long long n, unsigned long long seed);
 int qmatmul_grad_input(const void *go, int dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
                        const __half *scale, const __half *zp, void *gi, int bits, int g, cudaStream_t st);
+
+// Token counts above this go to the tensor-core GEMM, the rest to the streaming kernel.
+constexpr int64_t TC_MIN_TOKENS = 32;
 
 static bool is_float_dtype(int dt) { return dt == BW_F32 || dt == BW_F16 || dt == BW_BF16; }
 
@@ -86,7 +96,11 @@ size_t bw_qmatmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int bits, int
     (void)N; (void)group_size;
     if (bits != 2 && bits != 4 && bits != 8) return 0;
     if (M <= 0 || K <= 0) return 0;
-    return smallm_workspace_bytes(M < 64 ? M : 64, K, bits);
+    const size_t small = smallm_workspace_bytes(M < 64 ? M : 64, K, bits);
+    if (M <= TC_MIN_TOKENS) return small;
+    // the tensor-core kernel reads fp16 activations; other dtypes are cast into the workspace
+    const size_t cast = tc_workspace_bytes(M, K);
+    return cast > small ? cast : small;
 }
 
 int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *qweight,
@@ -113,6 +127,8 @@ int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
         return qmatmul_smallm(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, nullptr, st);
     if (!workspace || workspace_bytes < bw_qmatmul_workspace_bytes(M, N, K, bits, group_size))
         return BW_ERR_WORKSPACE;
+    if (M > TC_MIN_TOKENS && tc_path_ok(M, N, K, qweight, bits, group_size))
+        return qmatmul_tc(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, workspace, st);
     // token blocks of at most 64 through the streaming kernel
     const size_t xs = dtype_size(x_dtype), os = dtype_size(out_dtype);
     for (int64_t m0 = 0; m0 < M; m0 += 64) {
@@ -211,9 +227,9 @@ const char *bw_last_cuda_error(void) { return g_cuda_error; }
 
 int bw_device_status(void) {
     if (cudaDeviceSynchronize() != cudaSuccess) return record_cuda_error(cudaGetLastError(), "cudaDeviceSynchronize");
-    const int v = rtn_device_status();
-    if (v < 0) return BW_ERR_CUDA;
-    return v ? BW_ERR_TIMEOUT : BW_OK;
+    const int v = rtn_device_status(), t = tc_device_status();
+    if (v < 0 || t < 0) return BW_ERR_CUDA;
+    return (v || t) ? BW_ERR_TIMEOUT : BW_OK;
 }
 int bw_version(void) { return 100; }
 const char *bw_last_qmatmul_kernel(void) { return g_last_kernel; }
@@ -221,6 +237,7 @@ const char *bw_last_qmatmul_kernel(void) { return g_last_kernel; }
 // Not in the public header: tuning hook used by the benchmark's sweep mode.
 BW_API void bw_debug_set_smallm_tuning(int rt, int warps, int splits) { set_smallm_tuning(rt, warps, splits); }
 BW_API void bw_debug_set_pdl(int on) { set_smallm_pdl(on); }
+BW_API void bw_debug_set_tc(int on) { set_tc_enabled(on); }
 BW_API void bw_debug_set_rtn_stream(int on) { set_rtn_stream(on); }
 // Test hook (allocates a counter; not for production callers): mismatches between the RTN
 // kernel's reciprocal-based division and IEEE division over n operand pairs.

@@ -73,6 +73,8 @@ def _declare(L):
     L.bw_debug_set_rtn_stream.restype = None
     L.bw_debug_div_self_check.argtypes = [ctypes.c_ulonglong, ctypes.c_ulonglong]
     L.bw_debug_div_self_check.restype = ctypes.c_longlong
+    L.bw_debug_set_tc.argtypes = [i32]
+    L.bw_debug_set_tc.restype = None
     L.bw_debug_set_pdl.argtypes = [i32]
     L.bw_debug_set_pdl.restype = None
 

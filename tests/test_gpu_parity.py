@@ -266,6 +266,53 @@ def test_forward_vs_oracle(case):
     assert float((acc.cpu() - ref_acc).abs().max()) <= 1e-5 * denom, case
 
 
+TC_CASES = [
+    # bits, g, M, N, K, bias  -- token counts above 32 run on the tcgen05 tensor-core kernel
+    (4, 128, 128, 128, 256, True), (4, 64, 33, 256, 512, False), (4, 32, 300, 200, 384, True),
+    (8, 128, 256, 384, 1024, True), (8, 16, 100, 72, 160, False), (2, 64, 512, 256, 2048, True),
+    (2, 32, 65, 40, 192, False), (4, 128, 1000, 130, 96, True), (4, 256, 129, 64, 1024, False),
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES, ids=lambda c: "b%d_g%d_M%d_N%d_K%d_%s" % c)
+def test_tensor_core_forward_vs_oracle(case):
+    bits, g, M, N, K, bias = case
+    q, s_h, z_h, b_h = _make_layer(hash(case) % 100000, N, K, bits, g, bias)
+    x = torch.from_numpy(synth.normal(777 + M, (M, K), 1.0)).half()
+    ref, ref_acc = oracle_forward(x, q, s_h, z_h, b_h, bits, g, want_acc=True)
+    dev = [t.to(DEV) if t is not None else None for t in (x, q, s_h, z_h, b_h)]
+    y = quantized_matmul_cuda(*dev, bits, g)
+    assert _lib.last_qmatmul_kernel() == "qmm_tc_kernel"
+    assert _lib.lib().bw_device_status() == 0, "a bounded wait of the tensor-core pipeline ran out"
+    assert_close_rms(as_f32(y), as_f32(ref), 1e-2, str(case))
+    acc = quantized_matmul_cuda(dev[0], dev[1], dev[2], dev[3], None, bits, g, out_dtype=torch.float32)
+    denom = max(float(ref_acc.abs().max()), 1e-30)
+    assert float((acc.cpu() - ref_acc).abs().max()) <= 1e-5 * denom, case
+    # bf16 / fp32 activations are cast to fp16 first, like the reference (modules.py:74)
+    yb = quantized_matmul_cuda(dev[0].to(torch.bfloat16), dev[1], dev[2], dev[3], dev[4], bits, g)
+    refb = oracle_forward(x.to(torch.bfloat16), q, s_h, z_h, b_h, bits, g)
+    assert_close_rms(as_f32(yb), as_f32(refb), 1e-2, str(case))
+
+
+@pytest.mark.parametrize("M", [512, 2048])
+@pytest.mark.parametrize("bits,g", [(4, 128), (2, 64)])
+def test_prefill_full_size_shape_against_gpu_dequant_matmul(M, bits, g):
+    # Llama-3-8B gate/up shape: the tensor-core kernel against "dequantize (bit-exact kernel)
+    # then matmul in fp32" on the same device
+    N, K = 14336, 4096
+    gen = torch.Generator(device=DEV).manual_seed(M + bits)
+    w = (torch.randn(N, K, device=DEV, generator=gen) * 0.02).to(torch.bfloat16)
+    q, s_h, z_h = quantize_rtn_to_module_buffers(w, bits, g)
+    w_h = dequantize_rtn(q, s_h, z_h, g, bits=bits, out_dtype=torch.float16)
+    x = torch.randn(M, K, device=DEV, generator=gen).half()
+    y = quantized_matmul_cuda(x, q, s_h, z_h, None, bits, g)
+    assert _lib.last_qmatmul_kernel() == "qmm_tc_kernel" and _lib.lib().bw_device_status() == 0
+    ref = x.float() @ w_h.float().T
+    assert_close_rms(as_f32(y), as_f32(ref), 1e-2)
+    acc = quantized_matmul_cuda(x, q, s_h, z_h, None, bits, g, out_dtype=torch.float32)
+    assert float((acc - ref).abs().max()) <= 2e-5 * float(ref.abs().max())   # both sides accumulate in fp32
+
+
 def test_forward_kernel_selection():
     q, s_h, z_h, b_h = _make_layer(5, 64, 256, 4, 128, False)
     x = torch.zeros(4, 256, dtype=torch.float16, device=DEV)
