@@ -10,15 +10,16 @@
 // used by up to 256 tokens of one CTA and the accumulator D^T[n, m] lives in 128 lanes x BN
 // fp32 columns of tensor memory.
 //
-// Warp roles in a CTA of 192 threads (one output tile of 128 weight rows x BN tokens):
+// Warp roles in a CTA of 320 threads (one output tile of 128 weight rows x BN tokens):
 //   warp 0       TMA producer: cp.async.bulk.tensor loads the [BN tokens x 64 k] fp16 tile of
 //                the activations (128-byte swizzle, no multicast) for each pipeline stage
 //   warp 1       allocates tensor memory; one elected lane issues tcgen05.mma (kind::f16,
 //                M=128, N=BN, K=16, four per stage) and commits stages / the accumulator
-//   warps 2..5   128 dequantization threads, one per weight row: stream that row's packed
-//                words (prefetched one stage ahead in registers), expand them to fp16 in
+//   warps 2..9   two groups of 128 dequantization threads (one per weight row; the groups take
+//                alternate pipeline stages): stream that row's packed
+//                words (prefetched one own stage ahead in registers), expand them to fp16 in
 //                natural k order and store them as the A operand in the canonical K-major
-//                128-byte-swizzled layout; afterwards the same four warps are the epilogue:
+//                128-byte-swizzled layout; afterwards the same warps are the epilogue:
 //                tcgen05.ld of their TMEM lane quadrant, fp16 rounding + bias, coalesced stores
 // Stages are handed over with mbarriers (full_a, full_b, empty, acc_full).  Every wait is
 // bounded: a wait that runs out records an error in g_tc_status, the CTA drains, frees its
@@ -34,7 +35,8 @@ namespace {
 constexpr int TC_BM = 128;        // weight rows per tile (MMA M)
 constexpr int TC_BK = 64;         // k per stage: 64 fp16 = one 128-byte swizzle row
 constexpr int TC_STAGES = 4;
-constexpr int TC_THREADS = 192;
+constexpr int TC_DQ_GROUPS = 2;   // dequantization warp groups (4 warps each) taking alternate stages
+constexpr int TC_THREADS = 64 + TC_DQ_GROUPS * 128;
 constexpr unsigned TC_WAIT_LIMIT = 1u << 22;   // polls of >= 20 ns each: gives up after ~0.1-1 s
 
 __device__ int g_tc_status = 0;
@@ -256,6 +258,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
     } else {
         // ---- dequantization threads (one weight row each), then epilogue ----
         const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
+        const int dgroup = (warp - 2) >> 2;              // this group expands stages dgroup, dgroup+2, ...
         const int row = quad * 32 + lane;                // tile row == TMEM lane
         int64_t n = (int64_t)n0 + row;
         const bool n_ok = n < p.N;
@@ -285,16 +288,16 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
                 }
             }
         };
-        prefetch(0);
+        if (dgroup < p.k_stages) prefetch(dgroup);
         bool ok = true;
-        for (int kt = 0; kt < p.k_stages; ++kt) {
+        for (int kt = dgroup; kt < p.k_stages; kt += TC_DQ_GROUPS) {
             const int s = kt % TC_STAGES;
             const unsigned ph = (unsigned)(kt / TC_STAGES) & 1u;
             uint32_t w[SG::WPS];
 #pragma unroll
             for (int i = 0; i < SG::VPS; ++i) { w[4 * i] = wv[i].x; w[4 * i + 1] = wv[i].y; w[4 * i + 2] = wv[i].z; w[4 * i + 3] = wv[i].w; }
             GroupConst gc_now[4] = {gcs[0], gcs[1], gcs[2], gcs[3]};
-            if (kt + 1 < p.k_stages) prefetch(kt + 1);
+            if (kt + TC_DQ_GROUPS < p.k_stages) prefetch(kt + TC_DQ_GROUPS);
             uint4 chunk[8];
             expand_stage<BITS>(w, gc_now, kt * TC_BK, p.g_shift, (kt * TC_BK) >> p.g_shift, chunk);
             ok = __all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u, abort_flag, 4));   // warp-uniform
@@ -310,7 +313,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
         if (__all_sync(0xffffffffu, ok && mbar_wait(acc_full, 0u, abort_flag, 5))) {
             tc_fence_after();
             const __half bias_h = (p.bias && n_ok) ? p.bias[n] : __float2half(0.0f);
-            for (int cb = 0; cb < bn / 32; ++cb) {
+            // the warp groups share the lane quadrants and split the token columns
+            const int nblk = bn / 32, per = (nblk + TC_DQ_GROUPS - 1) / TC_DQ_GROUPS;
+            for (int cb = dgroup * per; cb < min(nblk, (dgroup + 1) * per); ++cb) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), r);
 #pragma unroll

@@ -270,7 +270,7 @@ TC_CASES = [
     # bits, g, M, N, K, bias  -- token counts above 32 run on the tcgen05 tensor-core kernel
     (4, 128, 128, 128, 256, True), (4, 64, 33, 256, 512, False), (4, 32, 300, 200, 384, True),
     (8, 128, 256, 384, 1024, True), (8, 16, 100, 72, 160, False), (2, 64, 512, 256, 2048, True),
-    (2, 32, 65, 40, 192, False), (4, 128, 1000, 130, 96, True), (4, 256, 129, 64, 1024, False),
+    (2, 32, 65, 40, 192, False), (4, 32, 1000, 130, 96, True), (4, 256, 129, 64, 1024, False),
 ]
 
 
