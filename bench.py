@@ -245,6 +245,7 @@ def run_decode8b(args, torch, dist, rank, world, device):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     value = bytes_per_step * args.steps * world / (ms * 1e-3) / 1e9
+    decode_kernel = _lib.last_qmatmul_kernel()
 
     # ---- end to end: pinned host activations in, host outputs back, per launch ----------
     hx = {M: {K: torch.randn(M, K).to(torch.bfloat16).pin_memory() for K in (4096, 14336)} for M in DECODE_M}
@@ -293,7 +294,7 @@ def run_decode8b(args, torch, dist, rank, world, device):
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps},
             "bytes_per_launch": bytes_per_step / (launches_per_step // 2), "launches_per_step": launches_per_step,
-            "breakdown": breakdown, "extra": extra, "kernel": _lib.last_qmatmul_kernel(),
+            "breakdown": breakdown, "extra": extra, "kernel": decode_kernel,
             "config": {"workload": "decode8b", "shapes": "Llama-3-8B linears x M{1,2,4,8,16}",
                        "bits": bits, "group_size": g, "layer_copies": args.layers,
                        "l2_policy": f"inputs larger than L2: {args.layers} distinct copies of every layer "

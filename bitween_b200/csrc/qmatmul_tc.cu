@@ -35,7 +35,7 @@ namespace {
 constexpr int TC_BM = 128;        // weight rows per tile (MMA M)
 constexpr int TC_BK = 64;         // k per stage: 64 fp16 = one 128-byte swizzle row
 constexpr int TC_STAGES = 4;
-constexpr int TC_DQ_GROUPS = 2;   // dequantization warp groups (4 warps each) taking alternate stages
+constexpr int TC_DQ_GROUPS = 4;   // dequantization warp groups (4 warps each) taking alternate stages
 constexpr int TC_THREADS = 64 + TC_DQ_GROUPS * 128;
 constexpr unsigned TC_WAIT_LIMIT = 1u << 22;   // polls of >= 20 ns each: gives up after ~0.1-1 s
 
