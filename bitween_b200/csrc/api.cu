@@ -36,6 +36,7 @@ bool tc_path_ok(int64_t M, int64_t N, int64_t K, const int32_t *q, int bits, int
 size_t tc_workspace_bytes(int64_t M, int64_t K);
 int tc_device_status();
 void set_tc_enabled(int on);
+void set_tc_splits(int s);
 int qmatmul_tc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
                const __half *scale, const __half *zp, const __half *bias, void *out, int out_dtype, int bits,
                int g, void *workspace, cudaStream_t st);
@@ -46,7 +47,8 @@ int qmatmul_grad_input(const void *go, int dtype, int64_t M, int64_t N, int64_t 
                        const __half *scale, const __half *zp, void *gi, int bits, int g, cudaStream_t st);
 
 // Token counts above this go to the tensor-core GEMM, the rest to the streaming kernel.
-constexpr int64_t TC_MIN_TOKENS = 32;
+static int64_t g_tc_min_tokens = 32;
+#define TC_MIN_TOKENS g_tc_min_tokens
 
 static bool is_float_dtype(int dt) { return dt == BW_F32 || dt == BW_F16 || dt == BW_BF16; }
 
@@ -238,6 +240,8 @@ const char *bw_last_qmatmul_kernel(void) { return g_last_kernel; }
 BW_API void bw_debug_set_smallm_tuning(int rt, int warps, int splits) { set_smallm_tuning(rt, warps, splits); }
 BW_API void bw_debug_set_pdl(int on) { set_smallm_pdl(on); }
 BW_API void bw_debug_set_tc(int on) { set_tc_enabled(on); }
+BW_API void bw_debug_set_tc_splits(int s) { set_tc_splits(s); }
+BW_API void bw_debug_set_tc_min_tokens(int m) { g_tc_min_tokens = m; }
 BW_API void bw_debug_set_rtn_stream(int on) { set_rtn_stream(on); }
 // Test hook (allocates a counter; not for production callers): mismatches between the RTN
 // kernel's reciprocal-based division and IEEE division over n operand pairs.

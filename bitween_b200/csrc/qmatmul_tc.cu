@@ -10,24 +10,32 @@
 // used by up to 256 tokens of one CTA and the accumulator D^T[n, m] lives in 128 lanes x BN
 // fp32 columns of tensor memory.
 //
-// Warp roles in a CTA of 320 threads (one output tile of 128 weight rows x BN tokens):
-//   warp 0       TMA producer: cp.async.bulk.tensor loads the [BN tokens x 64 k] fp16 tile of
-//                the activations (128-byte swizzle, no multicast) for each pipeline stage
+// Warp roles in a CTA of 576 threads (one output tile of 128 weight rows x BN tokens, BN from
+// 16 to 256 by token count):
+//   warp 0       TMA producer (one lane): cp.async.bulk.tensor loads, without multicast, of
+//                the [BN tokens x 64 k] fp16 activation tile (128-byte swizzle) of each k-stage
+//                and -- for small token tiles -- of the [128 rows x 64 k] tile of packed words,
+//                in two independent shared-memory rings
 //   warp 1       allocates tensor memory; one elected lane issues tcgen05.mma (kind::f16,
 //                M=128, N=BN, K=16, four per stage) and commits stages / the accumulator
-//   warps 2..9   two groups of 128 dequantization threads (one per weight row; the groups take
-//                alternate pipeline stages): stream that row's packed
-//                words (prefetched one own stage ahead in registers), expand them to fp16 in
-//                natural k order and store them as the A operand in the canonical K-major
-//                128-byte-swizzled layout; afterwards the same warps are the epilogue:
+//   warps 2..17  four groups of 128 dequantization threads (one per weight row; group g takes
+//                k-stages g, g+4, ...): fetch the row's packed words (register prefetch one
+//                own stage ahead for large tiles, the TMA ring for small ones), expand them to
+//                fp16 in natural k order and store them as the A operand in the canonical
+//                K-major 128-byte-swizzled layout; afterwards the same warps are the epilogue:
 //                tcgen05.ld of their TMEM lane quadrant, fp16 rounding + bias, coalesced stores
-// Stages are handed over with mbarriers (full_a, full_b, empty, acc_full).  Every wait is
+// Small problems split K over the CTAs of a thread-block cluster; the partial tiles are summed
+// through distributed shared memory.  Stages are handed over with mbarriers; every wait is
 // bounded: a wait that runs out records an error in g_tc_status, the CTA drains, frees its
-// tensor memory and returns.
+// tensor memory and returns.  Ring positions and phases are tracked with counters (a division
+// per stage on the single MMA-issuing thread cost 15 % of the throughput).
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "bw_common.cuh"
 #include "qmm_dequant.cuh"
+
+namespace cgx = cooperative_groups;
 
 namespace bw {
 namespace {
@@ -37,6 +45,7 @@ constexpr int TC_BK = 64;         // k per stage: 64 fp16 = one 128-byte swizzle
 constexpr int TC_STAGES = 4;
 constexpr int TC_DQ_GROUPS = 4;   // dequantization warp groups (4 warps each) taking alternate stages
 constexpr int TC_THREADS = 64 + TC_DQ_GROUPS * 128;
+static_assert(TC_STAGES == TC_DQ_GROUPS, "each dequantization group owns one A stage");
 constexpr unsigned TC_WAIT_LIMIT = 1u << 22;   // polls of >= 20 ns each: gives up after ~0.1-1 s
 
 __device__ int g_tc_status = 0;
@@ -127,11 +136,12 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t addr) {
     d |= (uint64_t)2 << 61;                           // bits [61,64): SWIZZLE_128B
     return d;
 }
-// Instruction descriptor for kind::f16: fp16 A and B (format 0), fp32 accumulator (1), both
-// operands K-major, M = 128, N = bn.
-__device__ __forceinline__ uint32_t umma_idesc_f16(int bn) {
+// Instruction descriptor for kind::f16: fp16 A (format 0), fp16 or bf16 B, fp32 accumulator
+// (1), both operands K-major, M = 128, N = bn.
+__device__ __forceinline__ uint32_t umma_idesc_f16(int bn, int b_is_bf16) {
     uint32_t d = 0;
     d |= 1u << 4;                                     // c_format = F32
+    d |= (b_is_bf16 ? 1u : 0u) << 10;                 // b_format: 0 = F16, 1 = BF16 (A stays F16)
     d |= (uint32_t)(bn >> 3) << 17;                   // n_dim
     d |= (uint32_t)(TC_BM >> 4) << 24;                // m_dim
     return d;
@@ -149,7 +159,13 @@ struct TcParams {
     int G;              // groups per row
     int words_per_row;  // K / vpi
     int k_stages;       // ceil(K / 64)
-    int bn;             // tokens per tile: 32, 64, 128 or 256
+    int bn;             // tokens per tile: 16, 32, 64, 128 or 256
+    int x_stages;       // depth of the TMA ring of activation tiles
+    int w_stages;       // depth of the TMA ring of packed-word tiles (a multiple of the dequant groups)
+    int splits;         // split-K factor = cluster size along grid z
+    int kper;           // k-stages per split
+    int x_is_bf16;      // always 0: kind::f16 MMAs take both operands in one 16-bit format
+    int w_direct;       // packed words by plain loads (large tiles) instead of the TMA ring
 };
 
 // Words of one row for one 64-k stage, as 16-byte vectors, and the natural-order expansion.
@@ -192,26 +208,35 @@ __device__ __forceinline__ void expand_stage(const uint32_t (&w)[StageGeom<BITS>
 
 template <int BITS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
+qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, const TcParams p) {
     using SG = StageGeom<BITS>;
+    constexpr int W_STAGE_BYTES = TC_BM * SG::WPS * 4;                    // packed words of 128 rows, one stage
     extern __shared__ unsigned char tc_smem_raw[];
     // 1024-byte alignment is required by the 128-byte swizzle pattern
     unsigned char *smem = tc_smem_raw + ((1024u - (smem_addr(tc_smem_raw) & 1023u)) & 1023u);
-    const int bn = p.bn;
-    unsigned char *a_tiles = smem;                                        // [STAGES][128][128 B]
-    unsigned char *b_tiles = smem + TC_STAGES * TC_BM * 128;              // [STAGES][bn][128 B]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(b_tiles + (size_t)TC_STAGES * bn * 128);
-    uint64_t *full_a = bars, *full_b = bars + TC_STAGES, *empty = bars + 2 * TC_STAGES, *acc_full = bars + 3 * TC_STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * TC_STAGES + 1);
+    const int bn = p.bn, NSX = p.x_stages, NSW = p.w_stages;
+    unsigned char *a_tiles = smem;                                        // [TC_STAGES][128][128 B]  fp16 weights
+    unsigned char *x_tiles = a_tiles + TC_STAGES * TC_BM * 128;           // [NSX][bn][128 B]         activations
+    unsigned char *w_tiles = x_tiles + (size_t)NSX * bn * 128;            // [NSW][128][WPS*4 B]      packed words
+    uint64_t *bars = reinterpret_cast<uint64_t *>(w_tiles + (size_t)NSW * W_STAGE_BYTES);
+    uint64_t *a_full = bars, *a_empty = bars + TC_STAGES, *x_full = bars + 2 * TC_STAGES;
+    uint64_t *x_empty = x_full + NSX, *w_full = x_empty + NSX, *w_empty = w_full + NSW, *acc_full = w_empty + NSW;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * TC_BM;
     const int m0 = blockIdx.y * bn;
+    // split-K over the CTAs of a cluster (grid z): this CTA owns k-stages [kt0, kt1)
+    const int kt0 = blockIdx.z * p.kper;
+    const int kt1 = min(kt0 + p.kper, p.k_stages);
+    const int nk = max(kt1 - kt0, 0);
     const uint32_t tmem_cols = bn < 32 ? 32u : (uint32_t)bn;
 
     if (tid == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full_a[s], 4); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&a_full[s], 4); mbar_init(&a_empty[s], 1); }   // a_full: the four warps of one group
+        for (int s = 0; s < NSX; ++s) { mbar_init(&x_full[s], 1); mbar_init(&x_empty[s], 1); }
+        for (int s = 0; s < NSW; ++s) { mbar_init(&w_full[s], 1); mbar_init(&w_empty[s], 4); }   // w_empty: 4 reader warps
         mbar_init(acc_full, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -224,58 +249,79 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ---- TMA producer: activations ----
+        // ---- TMA producer: two independent rings, activations and packed weight words ----
+        // (the small packed-word stages are freed by the dequantization warps as soon as they
+        // have been read into registers, so this ring runs far ahead of the tensor core)
         if (lane == 0) {
-            for (int kt = 0; kt < p.k_stages; ++kt) {
-                const int s = kt % TC_STAGES;
-                const unsigned ph = (unsigned)(kt / TC_STAGES) & 1u;
-                if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, 1)) break;
-                mbar_expect_tx(&full_b[s], (unsigned)bn * 128u);
-                tma_load_2d(b_tiles + (size_t)s * bn * 128, &x_map, kt * TC_BK, m0, &full_b[s]);
+            int ix = 0, iw = p.w_direct ? nk : 0;   // large tiles read packed words with plain loads
+            int sx = 0, sw = 0;                     // ring slots and phases advance without divisions
+            unsigned phx = 0, phw = 0, idle = 0;
+            while (ix < nk || iw < nk) {
+                bool progressed = false;
+                if (iw < nk) {
+                    const int s = sw;
+                    if (mbar_try_wait(&w_empty[s], phw ^ 1u)) {
+                        mbar_expect_tx(&w_full[s], (unsigned)W_STAGE_BYTES);
+                        tma_load_2d(w_tiles + (size_t)s * W_STAGE_BYTES, &w_map, (kt0 + iw) * SG::WPS, n0, &w_full[s]);
+                        ++iw;
+                        if (++sw == NSW) { sw = 0; phw ^= 1u; }
+                        progressed = true;
+                    }
+                }
+                if (ix < nk) {
+                    const int s = sx;
+                    if (mbar_try_wait(&x_empty[s], phx ^ 1u)) {
+                        mbar_expect_tx(&x_full[s], (unsigned)bn * 128u);
+                        tma_load_2d(x_tiles + (size_t)s * bn * 128, &x_map, (kt0 + ix) * TC_BK, m0, &x_full[s]);
+                        ++ix;
+                        if (++sx == NSX) { sx = 0; phx ^= 1u; }
+                        progressed = true;
+                    }
+                }
+                if (progressed) { idle = 0; continue; }
+                if (*abort_flag) break;
+                __nanosleep(20);
+                if (++idle > TC_WAIT_LIMIT) { *abort_flag = 1; atomicExch(&g_tc_status, 1); break; }
             }
         }
     } else if (warp == 1) {
         // ---- MMA issuer ----
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_f16(bn);
+            const uint32_t idesc = umma_idesc_f16(bn, p.x_is_bf16);
             bool ok = true;
-            for (int kt = 0; kt < p.k_stages && ok; ++kt) {
-                const int s = kt % TC_STAGES;
-                const unsigned ph = (unsigned)(kt / TC_STAGES) & 1u;
-                ok = mbar_wait(&full_a[s], ph, abort_flag, 2) && mbar_wait(&full_b[s], ph, abort_flag, 3);
+            int si = 0;
+            unsigned phx = 0;
+            for (int i = 0; i < nk && ok; ++i) {
+                const int sa = i % TC_STAGES;
+                ok = mbar_wait(&a_full[sa], (unsigned)(i / TC_STAGES) & 1u, abort_flag, 2) &&
+                     mbar_wait(&x_full[si], phx, abort_flag, 3);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_addr = smem_addr(a_tiles + (size_t)s * TC_BM * 128);
-                const uint32_t b_addr = smem_addr(b_tiles + (size_t)s * bn * 128);
+                const uint32_t a_addr = smem_addr(a_tiles + (size_t)sa * TC_BM * 128);
+                const uint32_t b_addr = smem_addr(x_tiles + (size_t)si * bn * 128);
 #pragma unroll
                 for (int k4 = 0; k4 < TC_BK / 16; ++k4)
                     umma_f16(tmem_base, umma_smem_desc(a_addr + k4 * 32), umma_smem_desc(b_addr + k4 * 32), idesc,
-                             (kt | k4) != 0 ? 1u : 0u);
-                umma_commit(&empty[s]);       // frees the stage once these MMAs have read it
+                             (i | k4) != 0 ? 1u : 0u);
+                umma_commit(&a_empty[sa]);     // both free once these MMAs have read their operands
+                umma_commit(&x_empty[si]);
+                if (++si == NSX) { si = 0; phx ^= 1u; }
             }
-            if (ok) umma_commit(acc_full);    // accumulator complete
+            if (ok) umma_commit(acc_full);     // accumulator complete (arrives at once when nk == 0)
         }
     } else {
         // ---- dequantization threads (one weight row each), then epilogue ----
         const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
-        const int dgroup = (warp - 2) >> 2;              // this group expands stages dgroup, dgroup+2, ...
+        const int dgroup = (warp - 2) >> 2;              // this group expands stages dgroup, dgroup+G, ...
         const int row = quad * 32 + lane;                // tile row == TMEM lane
         int64_t n = (int64_t)n0 + row;
         const bool n_ok = n < p.N;
         if (!n_ok) n = p.N - 1;
-        const uint4 *qrow = reinterpret_cast<const uint4 *>(p.q + n * p.words_per_row);
         const __half *srow = p.scale + n * p.G, *zrow = p.zp + n * p.G;
-        const int vec_per_row = p.words_per_row >> 2;
         const int gps = max(1, TC_BK >> p.g_shift);      // groups per stage (<= 4)
 
-        uint4 wv[SG::VPS];
         GroupConst gcs[4];
-        auto prefetch = [&](int kt) {
-#pragma unroll
-            for (int i = 0; i < SG::VPS; ++i) {
-                const int v = min(kt * SG::VPS + i, vec_per_row - 1);   // past-the-end k meets zero activations
-                wv[i] = __ldg(qrow + v);
-            }
+        auto prefetch_consts = [&](int kt) {             // kt = global k-stage index
             const int grp0 = (kt * TC_BK) >> p.g_shift;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -288,54 +334,132 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const TcParams p) {
                 }
             }
         };
-        if (dgroup < p.k_stages) prefetch(dgroup);
-        bool ok = true;
-        for (int kt = dgroup; kt < p.k_stages; kt += TC_DQ_GROUPS) {
-            const int s = kt % TC_STAGES;
-            const unsigned ph = (unsigned)(kt / TC_STAGES) & 1u;
-            uint32_t w[SG::WPS];
+        // Packed words: for large token tiles the MMA time per stage hides global-load latency, so
+        // each thread simply prefetches its row's next stage into registers (cheapest in
+        // instructions); for small tiles the words come through the deep TMA ring.
+        const uint4 *qrow = reinterpret_cast<const uint4 *>(p.q + n * p.words_per_row);
+        const int vec_per_row = p.words_per_row >> 2;
+        uint4 wv[SG::VPS];
+        auto prefetch_words = [&](int kt) {
 #pragma unroll
-            for (int i = 0; i < SG::VPS; ++i) { w[4 * i] = wv[i].x; w[4 * i + 1] = wv[i].y; w[4 * i + 2] = wv[i].z; w[4 * i + 3] = wv[i].w; }
+            for (int v = 0; v < SG::VPS; ++v)
+                wv[v] = __ldg(qrow + min(kt * SG::VPS + v, vec_per_row - 1));   // past-the-end k meets zero activations
+        };
+        if (dgroup < nk) {
+            prefetch_consts(kt0 + dgroup);
+            if (p.w_direct) prefetch_words(kt0 + dgroup);
+        }
+        bool ok = true;
+        int si = dgroup;                                 // slot in the packed-word ring (NSW % groups == 0)
+        unsigned phw = 0;
+        for (int i = dgroup; i < nk; i += TC_DQ_GROUPS) {
+            const int sa = i % TC_STAGES;
+            const int kt = kt0 + i;
             GroupConst gc_now[4] = {gcs[0], gcs[1], gcs[2], gcs[3]};
-            if (kt + TC_DQ_GROUPS < p.k_stages) prefetch(kt + TC_DQ_GROUPS);
+            if (i + TC_DQ_GROUPS < nk) prefetch_consts(kt + TC_DQ_GROUPS);
+            uint32_t w[SG::WPS];
+            if (p.w_direct) {
+#pragma unroll
+                for (int v = 0; v < SG::VPS; ++v) { w[4 * v] = wv[v].x; w[4 * v + 1] = wv[v].y; w[4 * v + 2] = wv[v].z; w[4 * v + 3] = wv[v].w; }
+                if (i + TC_DQ_GROUPS < nk) prefetch_words(kt + TC_DQ_GROUPS);
+            } else {
+                ok = __all_sync(0xffffffffu, mbar_wait(&w_full[si], phw, abort_flag, 6));
+                if (!ok) break;
+                const uint4 *src = reinterpret_cast<const uint4 *>(w_tiles + (size_t)si * W_STAGE_BYTES + (size_t)row * SG::WPS * 4);
+#pragma unroll
+                for (int v = 0; v < SG::VPS; ++v) {
+                    const uint4 t = src[v];
+                    w[4 * v] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&w_empty[si]);    // the packed words are in registers now
+            }
             uint4 chunk[8];
             expand_stage<BITS>(w, gc_now, kt * TC_BK, p.g_shift, (kt * TC_BK) >> p.g_shift, chunk);
-            ok = __all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u, abort_flag, 4));   // warp-uniform
+            ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[sa], ((unsigned)(i / TC_STAGES) & 1u) ^ 1u, abort_flag, 4));
             if (!ok) break;
-            uint4 *arow = reinterpret_cast<uint4 *>(a_tiles + (size_t)s * TC_BM * 128 + (size_t)row * 128);
+            uint4 *arow = reinterpret_cast<uint4 *>(a_tiles + (size_t)sa * TC_BM * 128 + (size_t)row * 128);
 #pragma unroll
             for (int c = 0; c < 8; ++c) arow[c ^ (row & 7)] = chunk[c];
             fence_proxy_async_smem();                    // generic-proxy stores -> visible to the tensor core
             __syncwarp();
-            if (lane == 0) mbar_arrive(&full_a[s]);
+            if (lane == 0) mbar_arrive(&a_full[sa]);
+            si += TC_DQ_GROUPS;
+            if (si >= NSW) { si -= NSW; phw ^= 1u; }
         }
         // ---- epilogue ----
-        if (__all_sync(0xffffffffu, ok && mbar_wait(acc_full, 0u, abort_flag, 5))) {
-            tc_fence_after();
-            const __half bias_h = (p.bias && n_ok) ? p.bias[n] : __float2half(0.0f);
-            // the warp groups share the lane quadrants and split the token columns
-            const int nblk = bn / 32, per = (nblk + TC_DQ_GROUPS - 1) / TC_DQ_GROUPS;
-            for (int cb = dgroup * per; cb < min(nblk, (dgroup + 1) * per); ++cb) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), r);
+        const bool acc_ok = __all_sync(0xffffffffu, ok && mbar_wait(acc_full, 0u, abort_flag, 5));
+        if (acc_ok) tc_fence_after();
+        const int nblk = bn < 32 ? 1 : bn / 32, per = (nblk + TC_DQ_GROUPS - 1) / TC_DQ_GROUPS;
+        const __half bias_h = (p.bias && n_ok) ? p.bias[n] : __float2half(0.0f);
+        auto store_out = [&](int64_t m, float v) {
+            if (p.out_dtype == BW_F16) {
+                __half c = __float2half_rn(v);
+                if (p.bias) c = __hadd(c, bias_h);
+                reinterpret_cast<__half *>(p.out)[m * p.N + n] = c;
+            } else {
+                if (p.bias) v += __half2float(bias_h);
+                if (p.out_dtype == BW_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[m * p.N + n] = __float2bfloat16_rn(v);
+                else reinterpret_cast<float *>(p.out)[m * p.N + n] = v;
+            }
+        };
+        if (p.splits == 1) {
+            if (acc_ok) {
+                // the warp groups share the lane quadrants and split the token columns
+                for (int cb = dgroup * per; cb < min(nblk, (dgroup + 1) * per); ++cb) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), r);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int64_t m = (int64_t)m0 + cb * 32 + j;
-                    if (n_ok && m < p.M) {
-                        float v = __uint_as_float(r[j]);
-                        if (p.out_dtype == BW_F16) {
-                            __half c = __float2half_rn(v);
-                            if (p.bias) c = __hadd(c, bias_h);
-                            reinterpret_cast<__half *>(p.out)[m * p.N + n] = c;
-                        } else {
-                            if (p.bias) v += __half2float(bias_h);
-                            if (p.out_dtype == BW_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[m * p.N + n] = __float2bfloat16_rn(v);
-                            else reinterpret_cast<float *>(p.out)[m * p.N + n] = v;
-                        }
+                    for (int j = 0; j < 32; ++j) {
+                        const int64_t m = (int64_t)m0 + cb * 32 + j;
+                        if (n_ok && m < p.M) store_out(m, __uint_as_float(r[j]));
+                    }
+                }
+            }
+        } else {
+            // split-K: park this CTA's partial tile in its own shared memory (the input ring
+            // is idle by now) as red[column][row]; the cluster sums it below
+            float *red = reinterpret_cast<float *>(x_tiles);
+            if (acc_ok) {
+                for (int cb = dgroup * per; cb < min(nblk, (dgroup + 1) * per); ++cb) {
+                    uint32_t r[32];
+                    if (nk > 0) tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), r);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) red[(cb * 32 + j) * TC_BM + row] = nk > 0 ? __uint_as_float(r[j]) : 0.0f;
+                }
+            }
+        }
+    }
+    if (p.splits > 1) {
+        // every thread of every CTA of the cluster reaches these barriers (also after an abort)
+        cgx::cluster_group cluster = cgx::this_cluster();
+        float *red = reinterpret_cast<float *>(x_tiles);
+        cluster.sync();
+        if (warp >= 2 && *abort_flag == 0) {
+            const int rank = (int)cluster.block_rank(), nranks = (int)cluster.num_blocks();
+            const int cols = bn < 32 ? 32 : bn;
+            const int per_rank = (cols + nranks - 1) / nranks;
+            const int row = (warp & 3) * 32 + lane, dgroup = (warp - 2) >> 2;
+            const int64_t n = (int64_t)n0 + row;
+            const __half bias_h = (p.bias && n < p.N) ? p.bias[n] : __float2half(0.0f);
+            for (int c = rank * per_rank + dgroup; c < min(cols, (rank + 1) * per_rank); c += TC_DQ_GROUPS) {
+                float v = 0.0f;
+                for (int q = 0; q < nranks; ++q) v += cluster.map_shared_rank(red, q)[c * TC_BM + row];
+                const int64_t m = (int64_t)m0 + c;
+                if (n < p.N && m < p.M) {
+                    if (p.out_dtype == BW_F16) {
+                        __half h = __float2half_rn(v);
+                        if (p.bias) h = __hadd(h, bias_h);
+                        reinterpret_cast<__half *>(p.out)[m * p.N + n] = h;
+                    } else {
+                        if (p.bias) v += __half2float(bias_h);
+                        if (p.out_dtype == BW_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[m * p.N + n] = __float2bfloat16_rn(v);
+                        else reinterpret_cast<float *>(p.out)[m * p.N + n] = v;
                     }
                 }
             }
         }
+        cluster.sync();   // keep shared memory alive until every peer has read it
     }
     tc_fence_before();
     __syncthreads();
@@ -360,6 +484,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+int g_tc_splits = 0;   // experiments: force the split-K factor (0 = automatic)
+
 EncodeTiledFn encode_tiled_fn() {
     static EncodeTiledFn fn = nullptr;
     if (!fn) {
@@ -373,9 +499,41 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 template <int BITS>
-int launch_tc(const CUtensorMap &map, const TcParams &p, cudaStream_t st) {
+int launch_tc(const CUtensorMap &xmap, const CUtensorMap &wmap, TcParams p, cudaStream_t st) {
+    using SG = StageGeom<BITS>;
     auto kern = qmm_tc_kernel<BITS>;
-    const size_t smem = (size_t)TC_STAGES * TC_BM * 128 + (size_t)TC_STAGES * p.bn * 128 + 256 + 1024;
+    const size_t w_stage = (size_t)TC_BM * SG::WPS * 4, x_stage = (size_t)p.bn * 128;
+    const size_t fixed = (size_t)TC_STAGES * TC_BM * 128 + 1024 /*alignment slack*/ + 1024 /*barriers*/;
+    // Packed-word ring: a multiple of the number of dequantization groups deep, so that each
+    // group meets the phases of "its" barriers one after the other (a waiter that skipped a
+    // phase could not tell phase k from phase k-2 by parity).
+    int nsw = (int)(((p.bn >= 128 ? 32 : 64) * 1024) / w_stage);
+    nsw -= nsw % TC_DQ_GROUPS;
+    if (nsw < TC_DQ_GROUPS) nsw = TC_DQ_GROUPS;
+    int nsx = (int)((227 * 1024 - fixed - (size_t)nsw * w_stage) / x_stage);
+    if (nsx > 16) nsx = 16;
+    if (nsx < 2) return BW_ERR_UNSUPPORTED;
+    p.w_direct = p.bn >= 128 ? 1 : 0;
+    if (p.w_direct) nsw = TC_DQ_GROUPS;   // ring unused: keep it minimal
+    nsx = (int)((227 * 1024 - fixed - (size_t)nsw * w_stage) / x_stage);
+    if (nsx > 16) nsx = 16;
+    p.x_stages = nsx;
+    p.w_stages = nsw;
+    // split-K (cluster along z) only for small tiles that would leave most SMs idle
+    const int64_t tiles = ((p.N + TC_BM - 1) / TC_BM) * ((p.M + p.bn - 1) / p.bn);
+    int splits = 1;
+    if (g_tc_splits > 0) splits = g_tc_splits;
+    else if (p.bn <= 64 && tiles < 148) {
+        splits = (int)(148 / tiles);
+        if (splits > 8) splits = 8;
+        if (splits > p.k_stages / 4) splits = p.k_stages / 4;
+        if (splits < 1) splits = 1;
+    }
+    const size_t red_bytes = (size_t)(p.bn < 32 ? 32 : p.bn) * TC_BM * 4;
+    if (splits > 8 || p.bn > 64 || red_bytes > (size_t)nsx * x_stage + (size_t)nsw * w_stage) splits = 1;
+    p.splits = splits;
+    p.kper = (p.k_stages + splits - 1) / splits;
+    const size_t smem = fixed + (size_t)nsx * x_stage + (size_t)nsw * w_stage;
     static size_t configured[64] = {};
     int dev = 0;
     BW_CUDA_TRY(cudaGetDevice(&dev));
@@ -383,15 +541,27 @@ int launch_tc(const CUtensorMap &map, const TcParams &p, cudaStream_t st) {
         BW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
-    const dim3 grid((unsigned)((p.N + TC_BM - 1) / TC_BM), (unsigned)((p.M + p.bn - 1) / p.bn), 1);
-    kern<<<grid, TC_THREADS, smem, st>>>(map, p);
-    return check_launch("qmm_tc_kernel");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((p.N + TC_BM - 1) / TC_BM), (unsigned)((p.M + p.bn - 1) / p.bn), (unsigned)splits);
+    cfg.blockDim = dim3(TC_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned)splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = splits > 1 ? 1 : 0;
+    BW_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, xmap, wmap, p));
+    return BW_OK;
 }
 
 }  // namespace
 
 static bool g_tc_enabled = true;
 void set_tc_enabled(int on) { g_tc_enabled = on != 0; }
+void set_tc_splits(int s) { g_tc_splits = s; }
 
 // Layout preconditions of the tensor-core kernel (others run on the streaming / general kernels).
 bool tc_path_ok(int64_t M, int64_t N, int64_t K, const int32_t *q, int bits, int g) {
@@ -421,7 +591,12 @@ int qmatmul_tc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
                const __half *scale, const __half *zp, const __half *bias, void *out, int out_dtype, int bits,
                int g, void *workspace, cudaStream_t st) {
     const __half *xh = reinterpret_cast<const __half *>(x);
-    if (x_dtype != BW_F16 || !aligned_to(x, 16)) {
+    // fp16 activations are read by TMA as they are; bf16 / fp32 (or misaligned) activations are
+    // cast to fp16 first, as the reference does (bitween/modules.py:74).  kind::f16 MMAs want
+    // both operands in the same 16-bit format: an fp16 A with a bf16 B raised an illegal
+    // instruction on sm_100a, so the B-format bit of the descriptor stays 0.
+    const bool direct = x_dtype == BW_F16 && aligned_to(x, 16);
+    if (!direct) {
         if (!workspace || !aligned_to(workspace, 16)) return BW_ERR_WORKSPACE;
         __half *y = reinterpret_cast<__half *>(workspace);
         const int64_t n = M * K;
@@ -444,23 +619,34 @@ int qmatmul_tc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
     p.G = (int)(K / g);
     p.words_per_row = (int)(K / (32 / bits));
     p.k_stages = (int)((K + TC_BK - 1) / TC_BK);
-    p.bn = M > 128 ? 256 : (M > 64 ? 128 : (M > 32 ? 64 : 32));
+    p.bn = M > 128 ? 256 : (M > 64 ? 128 : (M > 32 ? 64 : (M > 16 ? 32 : 16)));
+    p.x_is_bf16 = (direct && x_dtype == BW_BF16) ? 1 : 0;
 
     CUtensorMap map;
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
     const cuuint64_t strides[1] = {(cuuint64_t)K * 2};                 // bytes between token rows
     const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)p.bn};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(xh), dims,
+    const CUresult r = encode_tiled_fn()(&map, p.x_is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(xh), dims,
                                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return BW_ERR_UNSUPPORTED;
+    // packed words: [N rows][K/vpi int32], one box = 128 rows x the words of one 64-k stage
+    CUtensorMap wmap;
+    const cuuint64_t wdims[2] = {(cuuint64_t)p.words_per_row, (cuuint64_t)N};
+    const cuuint64_t wstrides[1] = {(cuuint64_t)p.words_per_row * 4};
+    const cuuint32_t wbox[2] = {(cuuint32_t)(TC_BK / (32 / bits)), (cuuint32_t)TC_BM};
+    const CUresult rw = encode_tiled_fn()(&wmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<int32_t *>(q), wdims,
+                                          wstrides, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rw != CUDA_SUCCESS) return BW_ERR_UNSUPPORTED;
     set_last_kernel("qmm_tc_kernel");
     switch (bits) {
-        case 2: return launch_tc<2>(map, p, st);
-        case 4: return launch_tc<4>(map, p, st);
-        default: return launch_tc<8>(map, p, st);
+        case 2: return launch_tc<2>(map, wmap, p, st);
+        case 4: return launch_tc<4>(map, wmap, p, st);
+        default: return launch_tc<8>(map, wmap, p, st);
     }
 }
 

@@ -65,18 +65,36 @@ def _declare(L):
     L.bw_last_qmatmul_kernel.restype = ctypes.c_char_p
     L.bw_version.argtypes = []
     L.bw_version.restype = i32
-    L.bw_debug_set_smallm_tuning.argtypes = [i32, i32, i32]
-    L.bw_debug_set_smallm_tuning.restype = None
+    if hasattr(L, "bw_debug_set_smallm_tuning"):
+        L.bw_debug_set_smallm_tuning.argtypes = [i32, i32, i32]
+    if hasattr(L, "bw_debug_set_smallm_tuning"):
+        L.bw_debug_set_smallm_tuning.restype = None
     L.bw_device_status.argtypes = []
     L.bw_device_status.restype = i32
-    L.bw_debug_set_rtn_stream.argtypes = [i32]
-    L.bw_debug_set_rtn_stream.restype = None
-    L.bw_debug_div_self_check.argtypes = [ctypes.c_ulonglong, ctypes.c_ulonglong]
-    L.bw_debug_div_self_check.restype = ctypes.c_longlong
-    L.bw_debug_set_tc.argtypes = [i32]
-    L.bw_debug_set_tc.restype = None
-    L.bw_debug_set_pdl.argtypes = [i32]
-    L.bw_debug_set_pdl.restype = None
+    if hasattr(L, "bw_debug_set_rtn_stream"):
+        L.bw_debug_set_rtn_stream.argtypes = [i32]
+    if hasattr(L, "bw_debug_set_rtn_stream"):
+        L.bw_debug_set_rtn_stream.restype = None
+    if hasattr(L, "bw_debug_div_self_check"):
+        L.bw_debug_div_self_check.argtypes = [ctypes.c_ulonglong, ctypes.c_ulonglong]
+    if hasattr(L, "bw_debug_div_self_check"):
+        L.bw_debug_div_self_check.restype = ctypes.c_longlong
+    if hasattr(L, "bw_debug_set_tc_splits"):
+        L.bw_debug_set_tc_splits.argtypes = [i32]
+    if hasattr(L, "bw_debug_set_tc_splits"):
+        L.bw_debug_set_tc_splits.restype = None
+    if hasattr(L, "bw_debug_set_tc_min_tokens"):
+        L.bw_debug_set_tc_min_tokens.argtypes = [i32]
+    if hasattr(L, "bw_debug_set_tc_min_tokens"):
+        L.bw_debug_set_tc_min_tokens.restype = None
+    if hasattr(L, "bw_debug_set_tc"):
+        L.bw_debug_set_tc.argtypes = [i32]
+    if hasattr(L, "bw_debug_set_tc"):
+        L.bw_debug_set_tc.restype = None
+    if hasattr(L, "bw_debug_set_pdl"):
+        L.bw_debug_set_pdl.argtypes = [i32]
+    if hasattr(L, "bw_debug_set_pdl"):
+        L.bw_debug_set_pdl.restype = None
 
 
 def lib():
