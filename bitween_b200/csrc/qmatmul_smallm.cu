@@ -44,6 +44,9 @@ namespace bw {
 namespace {
 
 constexpr int PF = 2;       // granularity of the activation/group-constant staging blocks
+#ifndef BW_SMALLM_THREADS
+#define BW_SMALLM_THREADS 1024
+#endif
 constexpr int STAGES = 4;   // depth of each warp's shared-memory ring of packed-word vectors
 
 struct SmallMParams {
@@ -186,7 +189,7 @@ __device__ __forceinline__ void stage_group_consts(const SmallMParams &p, int64_
 template <int MT, int RT, int WARPS> struct Occupancy {
     // CTAs per SM the register allocator should leave room for: 64 registers per thread for
     // one row tile and up to 16 tokens, 128 otherwise.
-    static constexpr int THREADS = (MT <= 2 && RT == 1) ? 1024 : ((MT <= 2) ? 512 : 256);
+    static constexpr int THREADS = (MT <= 2 && RT == 1) ? BW_SMALLM_THREADS : ((MT <= 2) ? 512 : 256);
     static constexpr int MIN_BLOCKS = THREADS / (WARPS * 32) > 0 ? THREADS / (WARPS * 32) : 1;
 };
 
@@ -255,14 +258,8 @@ qmm_smallm_kernel(const SmallMParams p) {
     for (int xb = 0; xb < nloc; xb += p.gblock) {     // p.gblock is a multiple of PF
         const int nb = min(p.gblock, nloc - xb);
         if (xb > 0) __syncthreads();   // every warp is done with the previous block's activations
-#if defined(BW_EXP) && (BW_EXP & 8)
-        if (false)
-#endif
         stage_group_consts<R, Geo::KC>(p, (int64_t)n0 + warp * R, c_first, stride, xb, nb, gpc, gcw, lane);
         if (xb == 0) pdl_wait();       // the prepared activations come from the preceding kernel
-#if defined(BW_EXP) && (BW_EXP & 8)
-        if (false)
-#endif
         {
             constexpr int VPC = Geo::NX * MT * 32;   // 16-byte vectors of activations per chunk
             for (int i = threadIdx.x; i < nb * VPC; i += WARPS * 32) {
@@ -308,22 +305,12 @@ qmm_smallm_kernel(const SmallMParams p) {
 #pragma unroll
                     for (int rt = 0; rt < RT; ++rt) {
                         uint32_t pa[4], pb[4];
-#if defined(BW_EXP) && (BW_EXP & 1)
-                        { const uint32_t wa = (&wv[rt * 2].x)[wi], wb = (&wv[rt * 2 + 1].x)[wi];
-                          pa[0] = wa; pa[1] = wa + 1; pa[2] = wa + 2; pa[3] = wa + 3; pb[0] = wb; pb[1] = wb + 1; pb[2] = wb + 2; pb[3] = wb + 3; }
-#else
                         dq[rt * 2][gs].run((&wv[rt * 2].x)[wi], pa);
                         dq[rt * 2 + 1][gs].run((&wv[rt * 2 + 1].x)[wi], pb);
-#endif
 #pragma unroll
                         for (int mt = 0; mt < MT; ++mt) {
-#if defined(BW_EXP) && (BW_EXP & 2)
-                            acc[rt][mt][0] += __uint_as_float(pa[0] ^ pb[0] ^ xf[mt].x); acc[rt][mt][1] += __uint_as_float(pa[1] ^ pb[1] ^ xf[mt].y);
-                            acc[rt][mt][2] += __uint_as_float(pa[2] ^ pb[2] ^ xf[mt].z); acc[rt][mt][3] += __uint_as_float(pa[3] ^ pb[3] ^ xf[mt].w);
-#else
                             mma_16816(acc[rt][mt], pa[0], pb[0], pa[1], pb[1], xf[mt].x, xf[mt].y);
                             mma_16816(acc[rt][mt], pa[2], pb[2], pa[3], pb[3], xf[mt].z, xf[mt].w);
-#endif
                         }
                     }
                 } else if constexpr (BITS == 8) {
@@ -385,11 +372,7 @@ qmm_smallm_kernel(const SmallMParams p) {
         }
     };
 
-#if defined(BW_EXP) && (BW_EXP & 4)
-    if (true) {
-#else
     if (p.splits == 1) {
-#endif
 #pragma unroll
         for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
