@@ -172,12 +172,21 @@ __device__ __forceinline__ void rtn_slot(float (&v)[Elems16<T>::V], int64_t c, b
     float s, zf; int32_t zi;
     uint32_t words[V >= VPI ? V / VPI : 1];
     bool fast = !group_bad;
+    float r = 0.0f;
     if (fast) {
-        group_params<T, NATIVE>(mn, mx, QMAX, floor_s, s, zi, zf);
-        fast = (s >= 9.094947e-13f) && (s <= 1.0995116e12f);   // 2^-40 <= scale <= 2^40
+        // group parameters with the same reciprocal+FMA division (the divisor Qmax is a constant)
+        constexpr float RQ = 1.0f / QMAX;                     // correctly rounded at compile time
+        s = rnd<T, NATIVE>(__fsub_rn(mx, mn));
+        s = rnd<T, NATIVE>(div_by_recip(s, QMAX, RQ));        // a range below 2^-79 ends at the floor anyway
+        if (s < floor_s) s = floor_s;
+        fast = (s >= 9.094947e-13f) && (s <= 1.0995116e12f);  // 2^-40 <= scale <= 2^40
+        r = __frcp_rn(s);
+        float z = rnd<T, NATIVE>(div_by_recip(-mn, s, r));    // |min| < 2^-79 gives |z| < 2^-39 -> 0 either way
+        z = fminf(fmaxf(rintf(z), 0.0f), QMAX);
+        zi = (int32_t)z;
+        zf = rnd<T, NATIVE>((float)zi);
     }
     if (fast) {
-        const float r = __frcp_rn(s);
         const int pos0 = (V >= VPI) ? 0 : (lane & (VPI / V - 1)) * V;
 #pragma unroll
         for (int wi = 0; wi < (V >= VPI ? V / VPI : 1); ++wi) {
@@ -519,10 +528,11 @@ __global__ void div_check_kernel(uint64_t n, uint64_t seed, unsigned long long *
         else if (kind == 3) mv = 0x7fffffu;
         else if (kind == 4) mv = ms;                   // quotient exactly 1 * 2^k
         else if (kind == 5) ms &= 0x7ff000u;           // short divisor significands (fp16/bf16 scales)
+        const float qconst = kind == 6 ? 15.0f : (kind == 7 ? 255.0f : (kind == 8 ? 3.0f : 0.0f));
         const int ev = 127 - 38 + (int)((z >> 46) % 77);   // |v| in [2^-38, 2^38]
         const int es = 127 - 39 + (int)((z >> 53) % 78);   // s in [2^-39, 2^38]
         const float v = __uint_as_float(((uint32_t)(z >> 45) & 1u) << 31 | (uint32_t)ev << 23 | mv);
-        const float s = __uint_as_float((uint32_t)es << 23 | ms);
+        const float s = qconst != 0.0f ? qconst : __uint_as_float((uint32_t)es << 23 | ms);   // Qmax divisors too
         const float a = div_by_recip(v, s, __frcp_rn(s)), b = __fdiv_rn(v, s);
         if (__float_as_uint(a) != __float_as_uint(b)) ++bad;
     }
