@@ -40,6 +40,14 @@ void set_tc_splits(int s);
 int qmatmul_tc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
                const __half *scale, const __half *zp, const __half *bias, void *out, int out_dtype, int bits,
                int g, void *workspace, cudaStream_t st);
+bool decode_path_ok(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
+                    const void *scale, const void *zp, int bits, int g);
+size_t decode_workspace_bytes(int64_t M, int64_t N, int64_t K, int bits);
+int decode_device_status();
+void set_decode_tuning(int enabled, int smem_kb, int max_ctas, int pdl);
+int qmatmul_decode(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
+                   const __half *scale, const __half *zp, const __half *bias, void *out, int out_dtype,
+                   int bits, int g, void *workspace, cudaStream_t st);
 int rtn_device_status();
 void set_rtn_stream(int on);
 long long div_self_check(unsigned long long n, unsigned long long seed);
@@ -90,12 +98,12 @@ int bw_dequantize(const int32_t *qweight, const void *scale, int scale_dtype, co
                       out_dtype, (cudaStream_t)stream);
 }
 
-size_t bw_qmatmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int bits, int group_size) {
-    // The streaming kernel reads activations that a preparation kernel has cast to fp16 and
-    // laid out in tensor-core fragment order: K (rounded up to a k-chunk) x 8*ceil(M/8) x 2
-    // bytes for one block of at most 64 tokens.  Split-K sums travel through distributed
-    // shared memory and need no global scratch.
-    (void)N; (void)group_size;
+// Scratch of the cluster split-K streaming kernel and the tensor-core GEMM (everything that
+// bw_qmatmul_noalloc can run).  The streaming kernel reads activations that a preparation
+// kernel has cast to fp16 and laid out in tensor-core fragment order: K (rounded up to a
+// k-chunk) x 8*ceil(M/8) x 2 bytes for one block of at most 64 tokens; its split-K sums travel
+// through distributed shared memory and need no global scratch.
+static size_t cluster_path_workspace_bytes(int64_t M, int64_t K, int bits) {
     if (bits != 2 && bits != 4 && bits != 8) return 0;
     if (M <= 0 || K <= 0) return 0;
     const size_t small = smallm_workspace_bytes(M < 64 ? M : 64, K, bits);
@@ -105,9 +113,22 @@ size_t bw_qmatmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int bits, int
     return cast > small ? cast : small;
 }
 
-int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *qweight,
-               const void *scale, const void *zero_point, const void *bias, void *out, int out_dtype,
-               int bits, int group_size, void *workspace, size_t workspace_bytes, void *stream) {
+size_t bw_qmatmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int bits, int group_size) {
+    (void)group_size;
+    const size_t base = cluster_path_workspace_bytes(M, K, bits);
+    if (base == 0 || M > 32 || N <= 0) return base;
+    // the persistent decode kernel adds row-block counters and stream-K partial tiles
+    const size_t dec = decode_workspace_bytes(M, N, K, bits);
+    return dec > base ? dec : base;
+}
+
+// `persistent_decode`: let M <= 32 run on the persistent TMA-fed decode kernel (needs the larger
+// workspace of bw_qmatmul_workspace_bytes); otherwise only the cluster split-K streaming kernel
+// and the tensor-core GEMM are used.
+static int qmatmul_dispatch(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *qweight,
+                            const void *scale, const void *zero_point, const void *bias, void *out, int out_dtype,
+                            int bits, int group_size, void *workspace, size_t workspace_bytes, void *stream,
+                            bool persistent_decode) {
     int rc = check_quant_shape(N, K, bits, group_size);
     if (rc != BW_OK) return rc;
     if (M < 0) return BW_ERR_SHAPE;
@@ -127,7 +148,13 @@ int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
     }
     if (!smallm_fast_path_ok(x, x_dtype, K, qweight, bits, group_size))
         return qmatmul_smallm(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, nullptr, st);
-    if (!workspace || workspace_bytes < bw_qmatmul_workspace_bytes(M, N, K, bits, group_size))
+    if (persistent_decode && M <= 32 && decode_path_ok(x, x_dtype, M, N, K, qweight, scale, zero_point, bits, group_size)) {
+        if (!workspace || workspace_bytes < bw_qmatmul_workspace_bytes(M, N, K, bits, group_size))
+            return BW_ERR_WORKSPACE;
+        rc = qmatmul_decode(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, workspace, st);
+        if (rc != BW_ERR_UNSUPPORTED) return rc;   // otherwise nothing was launched: use the cluster split-K kernel
+    }
+    if (!workspace || workspace_bytes < cluster_path_workspace_bytes(M, K, bits))
         return BW_ERR_WORKSPACE;
     if (M > TC_MIN_TOKENS && tc_path_ok(M, N, K, qweight, bits, group_size))
         return qmatmul_tc(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, workspace, st);
@@ -140,6 +167,13 @@ int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
         if (rc != BW_OK) return rc;
     }
     return BW_OK;
+}
+
+int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *qweight,
+               const void *scale, const void *zero_point, const void *bias, void *out, int out_dtype,
+               int bits, int group_size, void *workspace, size_t workspace_bytes, void *stream) {
+    return qmatmul_dispatch(x, x_dtype, M, N, K, qweight, scale, zero_point, bias, out, out_dtype, bits,
+                            group_size, workspace, workspace_bytes, stream, true);
 }
 
 int bw_qmatmul_noalloc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K,
@@ -155,9 +189,9 @@ int bw_qmatmul_noalloc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t
     size_t scratch_bytes = 0;
     rc = noalloc_scratch(&scratch, &scratch_bytes);
     if (rc != BW_OK) return rc;
-    if (bw_qmatmul_workspace_bytes(M, N, K, bits, group_size) > scratch_bytes) return BW_ERR_TOO_LARGE;
-    return bw_qmatmul(x, x_dtype, M, N, K, qweight, scale, zero_point, bias, out, out_dtype, bits,
-                      group_size, scratch, scratch_bytes, stream);
+    if (cluster_path_workspace_bytes(M, K, bits) > scratch_bytes) return BW_ERR_TOO_LARGE;
+    return qmatmul_dispatch(x, x_dtype, M, N, K, qweight, scale, zero_point, bias, out, out_dtype, bits,
+                            group_size, scratch, scratch_bytes, stream, false);
 }
 
 size_t bw_qmatmul_noalloc_max_scratch_bytes(void) {
@@ -229,9 +263,9 @@ const char *bw_last_cuda_error(void) { return g_cuda_error; }
 
 int bw_device_status(void) {
     if (cudaDeviceSynchronize() != cudaSuccess) return record_cuda_error(cudaGetLastError(), "cudaDeviceSynchronize");
-    const int v = rtn_device_status(), t = tc_device_status();
-    if (v < 0 || t < 0) return BW_ERR_CUDA;
-    return (v || t) ? BW_ERR_TIMEOUT : BW_OK;
+    const int v = rtn_device_status(), t = tc_device_status(), d = decode_device_status();
+    if (v < 0 || t < 0 || d < 0) return BW_ERR_CUDA;
+    return (v || t || d) ? BW_ERR_TIMEOUT : BW_OK;
 }
 int bw_version(void) { return 100; }
 const char *bw_last_qmatmul_kernel(void) { return g_last_kernel; }
@@ -239,6 +273,7 @@ const char *bw_last_qmatmul_kernel(void) { return g_last_kernel; }
 // Not in the public header: tuning hook used by the benchmark's sweep mode.
 BW_API void bw_debug_set_smallm_tuning(int rt, int warps, int splits) { set_smallm_tuning(rt, warps, splits); }
 BW_API void bw_debug_set_pdl(int on) { set_smallm_pdl(on); }
+BW_API void bw_debug_set_decode(int enabled, int smem_kb, int max_ctas, int pdl) { set_decode_tuning(enabled, smem_kb, max_ctas, pdl); }
 BW_API void bw_debug_set_tc(int on) { set_tc_enabled(on); }
 BW_API void bw_debug_set_tc_splits(int s) { set_tc_splits(s); }
 BW_API void bw_debug_set_tc_min_tokens(int m) { g_tc_min_tokens = m; }

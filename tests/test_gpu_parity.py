@@ -322,6 +322,10 @@ def test_forward_kernel_selection():
     x = torch.zeros(4, 96, dtype=torch.float16, device=DEV)
     quantized_matmul_cuda(x, q.to(DEV), s_h.to(DEV), z_h.to(DEV), None, 4, 24)
     assert _lib.last_qmatmul_kernel() == "qmm_general_kernel"
+    q, s_h, z_h, b_h = _make_layer(7, 256, 1024, 4, 128, False)
+    x = torch.zeros(4, 1024, dtype=torch.float16, device=DEV)
+    quantized_matmul_cuda(x, q.to(DEV), s_h.to(DEV), z_h.to(DEV), None, 4, 128)
+    assert _lib.last_qmatmul_kernel() == "qmm_decode_kernel"
 
 
 @pytest.mark.parametrize("xdt", [torch.float32, torch.bfloat16])
@@ -410,6 +414,45 @@ def test_decode_full_size_shapes_against_gpu_dequant_matmul(bits, g, shape):
     y = quantized_matmul_cuda(x, q, s_h, z_h, None, bits, g)
     ref = oracle_forward(x.cpu(), q[rows].cpu(), s_h[rows].cpu(), z_h[rows].cpu(), None, bits, g)
     assert_close_rms(as_f32(y[:, rows]), as_f32(ref), 1e-2)
+
+
+DECODE_CASES = [
+    # bits, g, M, N, K, bias -- shapes the persistent TMA-fed decode kernel takes (M <= 32, K/g a
+    # multiple of 8): cluster splits of a row block (few row blocks), whole row blocks, stream-K
+    # splits with shares in the global scratch (more row blocks than SMs), ragged N and K tails
+    (4, 128, 1, 1024, 4096, True), (4, 128, 8, 512, 2048, False), (4, 128, 13, 1000, 1024, True),
+    (4, 64, 32, 300, 1536, True), (4, 32, 5, 130, 768, False), (4, 128, 16, 14336, 1024, False),
+    (4, 128, 3, 20000, 1024, True), (4, 128, 24, 19100, 2048, False),
+    (8, 128, 1, 640, 2048, True), (8, 16, 9, 96, 384, False), (8, 64, 32, 20480, 512, True),
+    (2, 64, 2, 256, 4096, False), (2, 128, 16, 1100, 2048, True), (2, 64, 30, 19300, 1024, False),
+]
+
+
+@pytest.mark.parametrize("case", DECODE_CASES, ids=lambda c: "b%d_g%d_M%d_N%d_K%d_%s" % c)
+def test_persistent_decode_kernel_vs_oracle(case):
+    bits, g, M, N, K, bias = case
+    q, s_h, z_h, b_h = _make_layer(hash(case) % 100000, N, K, bits, g, bias)
+    x = torch.from_numpy(synth.normal(99 + M, (M, K), 1.0)).half()
+    ref, ref_acc = oracle_forward(x, q, s_h, z_h, b_h, bits, g, want_acc=True)
+    dev = [t.to(DEV) if t is not None else None for t in (x, q, s_h, z_h, b_h)]
+    y = quantized_matmul_cuda(*dev, bits, g)
+    assert _lib.last_qmatmul_kernel() == "qmm_decode_kernel"
+    assert _lib.lib().bw_device_status() == 0, "a bounded wait of the decode pipeline ran out"
+    assert_close_rms(as_f32(y), as_f32(ref), 1e-2, str(case))
+    acc = quantized_matmul_cuda(dev[0], dev[1], dev[2], dev[3], None, bits, g, out_dtype=torch.float32)
+    denom = max(float(ref_acc.abs().max()), 1e-30)
+    assert float((acc.cpu() - ref_acc).abs().max()) <= 1e-5 * denom, case
+    # the summation order is fixed: a second run gives the same bits
+    assert torch.equal(acc, quantized_matmul_cuda(dev[0], dev[1], dev[2], dev[3], None, bits, g, out_dtype=torch.float32))
+    # bf16 / fp32 activations are cast to fp16 inside the kernel, like the reference (modules.py:74)
+    for xdt in (torch.bfloat16, torch.float32):
+        xs = torch.from_numpy(synth.normal(7 + M, (M, K), 1.0)).to(xdt)
+        yb = quantized_matmul_cuda(xs.to(DEV), dev[1], dev[2], dev[3], dev[4], bits, g)
+        # (32 tokens of fp32 activations at 2 bits need more shared memory per stage than a ring
+        # of two stages leaves: that one combination runs on the cluster split-K kernel)
+        assert _lib.last_qmatmul_kernel() in ("qmm_decode_kernel", "qmm_smallm_kernel")
+        refb = oracle_forward(xs, q, s_h, z_h, b_h, bits, g)
+        assert_close_rms(as_f32(yb), as_f32(refb), 1e-2, str(case))
 
 
 # --------------------------------------------------------------------------- backward

@@ -1,8 +1,11 @@
 """bw_qmatmul_noalloc: the entry point for callers that cannot allocate device memory (code
 inside a CUDA-graph capture, allocation-free serving loops, plugins that are only handed
 buffers).  Its scratch is a fixed array inside the library instead of a caller workspace, so
-the results must equal those of the regular entry point -- also on a second call that finds
-the first call's data still in the scratch -- and oversized requests must be refused.
+the results must agree with those of the regular entry point -- also on a second call that
+finds the first call's data still in the scratch -- and oversized requests must be refused.
+(For up to 32 tokens the regular entry point may run the persistent decode kernel, which sums
+in another order; there the bar is the suite's 16-bit tolerance plus bit-equality of the
+no-allocation entry point with itself whatever the scratch held before.)
 
 Collected last on purpose (file name), so a run that stops at the first failure has already
 exercised every other test."""
@@ -33,17 +36,20 @@ def test_noalloc_matches_regular_entry_point_on_two_calls_in_a_row():
     bias = torch.from_numpy(synth.normal(2, (320,), 0.02)).half().to(DEV)
     # first call: 16 tokens; second call: 3 tokens of other data -> the scratch still holds the
     # first call's 16-token layout and must be fully rewritten, padding included
-    for call, (M, seed, xdt) in enumerate(((16, 3, torch.float16), (3, 4, torch.bfloat16))):
+    first = {}
+    for call, (M, seed, xdt) in enumerate(((16, 3, torch.float16), (3, 4, torch.bfloat16), (16, 3, torch.float16))):
         x = torch.from_numpy(synth.normal(seed, (M, 1024), 1.0)).to(xdt).to(DEV)
         ref = quantized_matmul_cuda(x, q, s, z, bias, 4, 128)
         out = torch.empty(M, 320, dtype=torch.float16, device=DEV)
         got = quantized_matmul_noalloc(x, q, s, z, bias, 4, 128, out)
         torch.cuda.synchronize()
         assert got.data_ptr() == out.data_ptr()
-        # same kernels, same inputs: the 16-bit tolerance of the suite (1e-2 * RMS) is the bar,
-        # and in fact the outputs are identical
+        # same inputs, same numerics contract: the 16-bit tolerance of the suite (1e-2 * RMS)
         assert_close_rms(as_f32(got), as_f32(ref), 1e-2, f"call {call}")
-        assert torch.equal(got, ref), f"call {call}"
+        # the third call repeats the first after the scratch held other data: identical bits
+        if (M, seed) in first:
+            assert torch.equal(got, first[(M, seed)]), f"call {call}"
+        first[(M, seed)] = got.clone()
     # a different bit width and several 64-token blocks reuse the same scratch
     q8, s8, z8 = _layer(5, 96, 512, 8, 32)
     x = torch.from_numpy(synth.normal(6, (130, 512), 1.0)).half().to(DEV)
