@@ -110,9 +110,18 @@ BW_API int bw_dequantize(const int32_t *qweight, const void *scale, int scale_dt
  *                   (bitween/modules.py:97,101); BW_BF16: bf16(acc + bias);
  *                   BW_F32: acc + bias with no 16-bit rounding (fp32-accumulate checks)
  *   workspace       device scratch of at least bw_qmatmul_workspace_bytes(...) bytes, or
- *                   NULL when that is 0.  Calls that overlap on the GPU must not share it.
- * Accumulation is fp32.  The kernel is chosen from M (small-M streaming kernel, large-M
- * tensor-core GEMM); unusual group sizes run on a slower general kernel, never on the CPU.
+ *                   NULL when that is 0.  Calls that overlap on the GPU must not share it,
+ *                   and a workspace address identifies the caller to the library (the
+ *                   decode kernel keeps its row-block counters per workspace address, for
+ *                   up to 16 addresses per device; further ones use the cluster kernel).
+ * Accumulation is fp32.  The kernel is chosen from M and the layout: up to 32 tokens run on
+ * the persistent TMA-fed decode kernel (one launch; needs K/group_size to be a multiple of 8
+ * and 16-byte aligned rows, else the cluster split-K streaming kernel runs), more on the
+ * tcgen05 tensor-core GEMM; unusual group sizes run on a slower general kernel, never on the
+ * CPU.  bw_qmatmul_workspace_bytes: the prepared activations of the cluster kernel (K rounded
+ * up to a k-chunk x 8*ceil(min(M,64)/8) x 2 bytes), the fp16 cast of the activations for the
+ * GEMM (M*K*2), or the decode kernel's row-block shares (320 x 8*ceil(M/8) x 128 x 4 bytes),
+ * whichever the call may need most.
  */
 BW_API size_t bw_qmatmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int bits, int group_size);
 
@@ -141,7 +150,8 @@ BW_API int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t 
  * All calls on a device share the array and it keeps the last call's contents; every call
  * rewrites the part it reads (padding included), so nothing has to be cleared, but calls that
  * overlap on the GPU (different streams) race on it -- issue them on one stream.
- * Arguments and results are exactly those of bw_qmatmul.
+ * Arguments and results are those of bw_qmatmul (same numerics; up to 32 tokens the sums may
+ * be added in another order than bw_qmatmul's decode kernel does, so the last bit can differ).
  */
 BW_API int bw_qmatmul_noalloc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K,
                        const int32_t *qweight, const void *scale, const void *zero_point,

@@ -41,6 +41,9 @@ def test_status_strings_and_argument_validation_need_no_gpu():
     assert L.bw_qmatmul(z, 1, 4, 8, 64, z, z, z, z, z, 1, 4, 32, z, 0, z) == 6
     assert L.bw_qmatmul(z, 1, 0, 8, 64, z, z, z, z, z, 1, 4, 32, z, 0, z) == 0
     assert L.bw_dequantize(z, z, 0, z, 3, 4, 64, 4, 32, z, 9, z) == 4
-    assert L.bw_qmatmul_workspace_bytes(16, 4096, 4096, 4, 128) == 4096 * 16 * 2
-    assert L.bw_qmatmul_workspace_bytes(1, 4096, 100, 4, 4) == 8 * 128 * 2
+    # up to 32 tokens: the decode kernel's row-block shares (2 x 160 slots of [8*ceil(M/8)][128] fp32)
+    assert L.bw_qmatmul_workspace_bytes(16, 4096, 4096, 4, 128) == 2 * 160 * 16 * 128 * 4
+    assert L.bw_qmatmul_workspace_bytes(1, 4096, 100, 4, 4) == 2 * 160 * 8 * 128 * 4
+    # more tokens: the fp16 cast of the activations for the tensor-core GEMM
+    assert L.bw_qmatmul_workspace_bytes(64, 4096, 4096, 4, 128) == 64 * 4096 * 2
     assert L.bw_qmatmul_workspace_bytes(0, 8, 64, 4, 32) == 0
