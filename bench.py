@@ -217,7 +217,8 @@ def run_decode8b(args, torch, dist, rank, world, device):
                 for L in stack:
                     quantized_matmul_cuda(xs[M][L.K], L.q, L.scale, L.zp, None, bits, g, out=outs[M][L.N])
 
-    launches_per_step = 2 * len(DECODE_M) * args.layers * len(LLAMA8B_SHAPES)   # preparation + streaming kernel
+    calls_per_step = len(DECODE_M) * args.layers * len(LLAMA8B_SHAPES)
+    launches_per_step = calls_per_step                      # the decode kernel is the only launch of a call
     bytes_per_step = sum(decode_bytes(M, N, K, bits, g) for M in DECODE_M for (_, N, K) in LLAMA8B_SHAPES) * args.layers
 
     for _ in range(max(args.warmup, 1) if not args.graph else 1):
@@ -290,10 +291,11 @@ def run_decode8b(args, torch, dist, rank, world, device):
     if rank == 0 and not args.no_extra:
         extra = run_extras(args, torch, fn, quantized_matmul_cuda, device, gen)
 
-    return {"value": value, "ms": ms, "launches": launches_per_step * args.steps, "clocks": clocks,
+    return {"value": value, "ms": ms, "launches": launches_per_step * args.steps, "calls": calls_per_step * args.steps,
+            "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps},
-            "bytes_per_launch": bytes_per_step / (launches_per_step // 2), "launches_per_step": launches_per_step,
+            "bytes_per_launch": bytes_per_step / calls_per_step, "launches_per_step": launches_per_step,
             "breakdown": breakdown, "extra": extra, "kernel": decode_kernel,
             "config": {"workload": "decode8b", "shapes": "Llama-3-8B linears x M{1,2,4,8,16}",
                        "bits": bits, "group_size": g, "layer_copies": args.layers,
@@ -386,9 +388,9 @@ def main():
 
     if rank == 0:
         peaks = read_peaks()
-        # one qmatmul call = preparation kernel + streaming kernel; the roofline is stated per
-        # streaming-kernel launch, its duration taken as the whole call's share of the timed region
-        ms_per_launch = res["ms"] / max(res["launches"] // 2, 1)
+        # the roofline is stated per qmatmul call (one launch of the dominant kernel, plus the
+        # activation cast where a call has one), its duration the call's share of the timed region
+        ms_per_launch = res["ms"] / max(res["calls"], 1)
         achieved = res["bytes_per_launch"] / (ms_per_launch * 1e-3) / 1e9
         line = {"metric": "w4g128_qmatmul_decode_GBps", "value": res["value"], "unit": "GB/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

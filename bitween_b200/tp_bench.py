@@ -47,7 +47,9 @@ def run_tp70b(args, torch_mod, dist, rank, world, device, ClockSampler, time_reg
                 if mode == "row" and dist is not None:
                     dist.all_reduce(y)
 
-    launches_per_step = layers_n * len(LINEARS) * 2          # preparation + streaming kernel per linear
+    # per linear: up to 32 tokens one decode kernel; above, the fp16 cast of the bf16 activations + the GEMM
+    kernels_per_call = 1 if M <= 32 else 2
+    launches_per_step = layers_n * len(LINEARS) * kernels_per_call
     bytes_per_step_rank = layers_n * sum(decode_bytes(M, n, k, bits, g) for (_, _, n, k, _, _, _) in layers[0])
     for _ in range(2):
         step()
@@ -98,7 +100,8 @@ def run_tp70b(args, torch_mod, dist, rank, world, device, ClockSampler, time_reg
         ms_e2e = float(t.item())
     h2d = layers_n * sum(2 * M * k for (_, _, n, k, _, _, _) in layers[0])
     d2h = layers_n * sum(2 * M * n for (_, _, n, k, _, _, _) in layers[0])
-    return {"value": value, "ms": ms, "launches": launches_per_step * args.steps, "clocks": clocks,
+    return {"value": value, "ms": ms, "launches": launches_per_step * args.steps,
+            "calls": layers_n * len(LINEARS) * args.steps, "clocks": clocks,
             "e2e": {"value": bytes_per_step_rank * world * e2e_steps / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "steps": e2e_steps},
             "bytes_per_launch": bytes_per_step_rank / (layers_n * len(LINEARS)),
