@@ -21,9 +21,11 @@
 //     magic-number dequantization and feeds mma.sync.m16n8k16 with the weights as the A operand
 //     (16 weight rows x 8 tokens);
 //   * warps 17..20 take the finished sums of each row-block share off the consumers' hands:
-//     whole row blocks are stored; shares go to a global scratch and the last CTA to arrive for
-//     a row block (a wrapping atomic counter per row block, in library-owned memory) sums them
-//     in CTA order.  No CTA ever waits for another.
+//     whole row blocks are stored; the CTAs of a row block that form a thread-block cluster
+//     exchange slices of their shares through distributed shared memory and each adds and
+//     stores one slice (rank order); stream-K shares go to a global scratch and the last CTA
+//     to arrive for a row block (a wrapping atomic counter per row block, in library-owned
+//     memory) sums them in CTA order.  Outside a cluster no CTA ever waits for another.
 // Every mbarrier wait is bounded; a wait that runs out records an error in g_dec_status and the
 // CTA stops waiting.
 #include <cuda.h>
@@ -76,6 +78,7 @@ struct DecParams {
     int stages;           // ring depth
     int raw_bytes;        // raw activation bytes per tile
     int cluster;          // CTAs per row block when they form a thread-block cluster (sums through DSMEM), else 1
+    int cluster_leader;   // 1: the cluster's first CTA collects the shares; 0: every CTA collects one slice
 };
 
 template <int BITS> struct DecGeom {
@@ -258,12 +261,12 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     uint64_t *full = reinterpret_cast<uint64_t *>(red + NRED * 2 * RED);
     uint64_t *empty = full + DK_MAX_STAGES;
     uint64_t *xdone = empty + DK_MAX_STAGES;                          // [S] activations of the stage are converted
-    uint64_t *cdone = xdone + DK_MAX_STAGES;                          // [1] the cluster's shares have arrived (leader CTA)
+    uint64_t *cdone = xdone + DK_MAX_STAGES;                          // [1] the peers' shares of this CTA's slice have arrived
     uint64_t *red_full = cdone + 1;                     // [2] consumers -> hand-over warps
     uint64_t *red_free = red_full + 2;                               // [2] hand-over warps -> consumers
     volatile int *flags = reinterpret_cast<volatile int *>(red_free + 2);   // [0] a wait ran out, [1] last arriver, [2] c_lo, [3] nc
     int *slots = const_cast<int *>(flags) + 4;                       // [DK_MAX_CTAS] scratch slots of one row block's shares
-    float4 *cpart = reinterpret_cast<float4 *>(                      // [cluster - 1][MTOK][128] shares of the other CTAs (leader CTA)
+    float4 *cpart = reinterpret_cast<float4 *>(                      // [cluster ranks][slice] the peers' shares of this CTA's slice of the outputs
         (reinterpret_cast<uintptr_t>(slots + DK_MAX_CTAS) + 15) & ~(uintptr_t)15);
     volatile int *dead = flags;
     const unsigned stage_tx = DK_W_BYTES + 2 * DK_C_BYTES + (unsigned)p.raw_bytes;
@@ -277,7 +280,7 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, DK_CWARPS); mbar_init(xdone + s, DK_CWARPS); }
         for (int b = 0; b < 2; ++b) { mbar_init(red_full + b, DK_CWARPS); mbar_init(red_free + b, 1); }
-        mbar_init(cdone, (unsigned)(p.cluster > 1 ? (p.cluster - 1) * DK_HTHREADS : 1));
+        mbar_init(cdone, (unsigned)(p.cluster > 1 ? (p.cluster - 1) * DK_HWARPS : 1));   // one arrival per peer hand-over warp
         flags[0] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -364,24 +367,28 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             }
             handover_sync();
             if (htid == 0) mbar_arrive(red_free + b);           // the consumers may refill this buffer
-            auto store4 = [&](int j) {
-                const int e = (htid + j * DK_HTHREADS) * 4;
+            auto store_f4 = [&](int idx, float4 val) {           // idx: float4 index into the [MTOK][128] tile
+                const int e = idx * 4;
                 const int m = e / DK_ROWS, r = e % DK_ROWS;
                 if (m < p.M) {
-                    if (nbase + r + 0 < p.N) store_out(m, nbase + r + 0, v[j].x);
-                    if (nbase + r + 1 < p.N) store_out(m, nbase + r + 1, v[j].y);
-                    if (nbase + r + 2 < p.N) store_out(m, nbase + r + 2, v[j].z);
-                    if (nbase + r + 3 < p.N) store_out(m, nbase + r + 3, v[j].w);
+                    if (nbase + r + 0 < p.N) store_out(m, nbase + r + 0, val.x);
+                    if (nbase + r + 1 < p.N) store_out(m, nbase + r + 1, val.y);
+                    if (nbase + r + 2 < p.N) store_out(m, nbase + r + 2, val.z);
+                    if (nbase + r + 3 < p.N) store_out(m, nbase + r + 3, val.w);
                 }
             };
-            if (p.cluster > 1) {
-                // this CTA's only share of its row block; the cluster's leader adds the shares in rank order
+            auto store4 = [&](int j) { store_f4(htid + j * DK_HTHREADS, v[j]); };
+            if (p.cluster > 1 && p.cluster_leader) {
+                // This CTA's only share of its row block.  Small shares go to the cluster's first
+                // CTA through distributed shared memory; it adds them in rank order and stores,
+                // while the other CTAs are already gone.
                 const uint32_t rank = cluster_rank();
                 if (rank != 0) {
                     const uint32_t dst = remote_smem(cpart + (size_t)(rank - 1) * (RED / 4), 0);
 #pragma unroll
                     for (int j = 0; j < V4; ++j) remote_store4(dst + (uint32_t)(htid + j * DK_HTHREADS) * 16u, v[j]);
-                    remote_arrive_release(remote_smem(cdone, 0));
+                    __syncwarp();                                    // the lanes' stores are ordered before lane 0's arrival
+                    if ((htid & 31) == 0) remote_arrive_release(remote_smem(cdone, 0));
                 } else {
                     unsigned tries = 0;
                     while (!mbar_test_cluster(cdone, 0u)) {
@@ -398,6 +405,39 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                     }
 #pragma unroll
                     for (int j = 0; j < V4; ++j) store4(j);
+                }
+            } else if (p.cluster > 1) {
+                // Large shares: the cluster's CTAs split the block's outputs into equal slices: every CTA sends slice d of its sums to CTA d through
+                // distributed shared memory, and CTA d adds the shares in rank order and stores.
+                const uint32_t rank = cluster_rank(), nranks = (uint32_t)p.cluster;
+                const int SL = RED / 4 / p.cluster;                  // float4 per slice
+#pragma unroll
+                for (int j = 0; j < V4; ++j) {
+                    const int idx = htid + j * DK_HTHREADS;
+                    const uint32_t d = (uint32_t)(idx / SL);
+                    float4 *slot = cpart + (size_t)rank * SL + (idx - (int)d * SL);
+                    if (d == rank) *slot = v[j];
+                    else remote_store4(remote_smem(slot, d), v[j]);
+                }
+                __syncwarp();                                        // the lanes' stores are ordered before lane 0's arrivals
+                if ((htid & 31) == 0) {
+                    for (uint32_t d = 0; d < nranks; ++d)
+                        if (d != rank) remote_arrive_release(remote_smem(cdone, d));
+                }
+                handover_sync();                                     // this CTA's own slice is in place
+                unsigned tries = 0;
+                while (!mbar_test_cluster(cdone, 0u)) {
+                    if (*dead) break;
+                    __nanosleep(20);
+                    if (++tries > DK_WAIT_LIMIT) { *dead = 7; atomicExch(&g_dec_status, 7); break; }
+                }
+                for (int o = htid; o < SL; o += DK_HTHREADS) {
+                    float4 a = cpart[o];
+                    for (uint32_t r = 1; r < nranks; ++r) {
+                        const float4 c = cpart[(size_t)r * SL + o];
+                        a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w;
+                    }
+                    store_f4((int)rank * SL + o, a);
                 }
             } else if (whole) {
 #pragma unroll
@@ -703,17 +743,17 @@ int launch_dec(const DecMaps &maps, DecParams p, cudaStream_t st) {
         if (ctas > g_dec.max_ctas) ctas = g_dec.max_ctas;
     } else if (g_dec.max_ctas == 0 && p.RB <= ctas) {
         // no more row blocks than SMs: give each row block the same number of CTAs, 1, 2, 4 or 8,
-        // launched as one thread-block cluster whose leader adds the shares through distributed
-        // shared memory (no round trips through L2)
+        // launched as one thread-block cluster that adds its shares through distributed shared
+        // memory (no round trips through L2)
         int per_rb = 1;
         while (per_rb * 2 <= 8 && p.RB * per_rb * 2 <= ctas && per_rb * 2 <= p.KT) per_rb *= 2;
         ctas = p.RB * per_rb;
-        // (when the leader's buffer for the other CTAs' shares would be too large, the shares go
-        // through the global scratch like those of a stream-K split)
-        if ((size_t)(per_rb - 1) * MT * 8 * DK_ROWS * 4 <= 32 * 1024) p.cluster = per_rb;
+        p.cluster = per_rb;
+        p.cluster_leader = (size_t)(per_rb - 1) * MT * 8 * DK_ROWS * 4 <= 32 * 1024 ? 1 : 0;
     }
     if (ctas > p.tiles) ctas = p.tiles;
-    const size_t cpart_bytes = p.cluster > 1 ? (size_t)(p.cluster - 1) * MT * 8 * DK_ROWS * 4 : 0;
+    // the first CTA's buffer for the other CTAs' shares, or one [MTOK][128] tile (ranks x slices)
+    const size_t cpart_bytes = p.cluster > 1 ? (size_t)(p.cluster_leader ? p.cluster - 1 : 1) * MT * 8 * DK_ROWS * 4 : 0;
     const size_t fixed = 1024 /*alignment slack*/ + (size_t)NRED * 2 * MT * 8 * DK_ROWS * 4 + (3 * DK_MAX_STAGES + 5) * 8 +
                          16 + DK_MAX_CTAS * 4 + cpart_bytes + 64;
     const size_t budget = (size_t)(g_dec.smem_kb > 0 ? g_dec.smem_kb : 224) * 1024;
