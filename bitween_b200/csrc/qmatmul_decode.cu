@@ -14,13 +14,13 @@
 //     activations of the tile's k range; completion on mbarriers, so no thread holds a load in
 //     flight.  Weights, scales and zero points are requested before griddepcontrol.wait, the
 //     activations after it (they may come from the preceding kernel);
-//   * warps 0..15 (8 row slices x 2 chunk parities) are the consumers.  Together they first cast
-//     the tile's raw activations to fp16 (as bitween/modules.py:74) into tensor-core fragment
-//     order, pairing values the way the dequantizer pairs codes; then each warp reads its part
-//     of the swizzled weight tile without bank conflicts, expands the codes with the exact
+//   * warps 17.. (2 for up to 8 tokens, else 4) cast each tile's raw activations to fp16 (as bitween/modules.py:74) into
+//     tensor-core fragment order, pairing values the way the dequantizer pairs codes;
+//   * warps 0..15 (8 row slices x 2 chunk parities) are the consumers: each reads its part of
+//     the swizzled weight tile without bank conflicts, expands the codes with the exact
 //     magic-number dequantization and feeds mma.sync.m16n8k16 with the weights as the A operand
 //     (16 weight rows x 8 tokens);
-//   * warps 17..20 take the finished sums of each row-block share off the consumers' hands:
+//   * the last 4 warps take the finished sums of each row-block share off the consumers' hands:
 //     whole row blocks are stored; the CTAs of a row block that form a thread-block cluster
 //     exchange slices of their shares through distributed shared memory and each adds and
 //     stores one slice (rank order); stream-K shares go to a global scratch and the last CTA
@@ -48,9 +48,14 @@ constexpr int DK_CWARPS = 16;                      // consumer warps
 constexpr int DK_HWARPS = 4;                       // hand-over warps (row-block sums -> outputs / scratch)
 constexpr int DK_HTHREADS = DK_HWARPS * 32;
 constexpr int DK_CTHREADS = DK_CWARPS * 32;
+// converter warps (raw activations -> fp16 fragments): 2 for one token tile, 4 for more
+template <int MT> struct DecWarps {
+    static constexpr int X = MT == 1 ? 2 : 4;                       // converter warps
+    static constexpr int HANDOVER0 = DK_CWARPS + 1 + X;             // first hand-over warp
+    static constexpr int THREADS = (DK_CWARPS + 1 + X + DK_HWARPS) * 32;
+};
 constexpr int DK_PRODUCER = DK_CWARPS;             // warp index of the producer
-constexpr int DK_HANDOVER0 = DK_CWARPS + 1;        // first hand-over warp
-constexpr int DK_THREADS = (DK_CWARPS + 1 + DK_HWARPS) * 32;
+constexpr int DK_CONVERTER0 = DK_CWARPS + 1;       // first converter warp
 constexpr int DK_MAX_CTAS = 160;                   // upper bound of the grid (sizes the scratch)
 constexpr int DK_MAX_STAGES = 12;
 constexpr int DK_XBOX = 256;                       // widest TMA box of raw activations (elements)
@@ -185,7 +190,7 @@ template <> __device__ __forceinline__ uint32_t x_pair_to_h2<__nv_bfloat16>(cons
 }
 template <> __device__ __forceinline__ uint32_t x_pair_to_h2<float>(const float *v) { return h2_as_u32(__floats2half2_rn(v[0], v[1])); }
 
-// The consumer threads convert one tile together: each takes units of UNIT consecutive k of one
+// The converter threads convert one tile together: each takes units of UNIT consecutive k of one
 // token slot, casts them to fp16, pairs the values the way the dequantizer pairs codes (c_j with
 // c_{j+vpi/2}) and stores them where the consuming lane reads them with one 16-byte load:
 //   xs[(block*MT + m/8)*32 + (((m%8)*4 + t) ^ (block & 7))],  block = parity*NXC + piece, chunk = 2*t + parity
@@ -194,14 +199,14 @@ template <> __device__ __forceinline__ uint32_t x_pair_to_h2<float>(const float 
 // The raw tile is [box][token slot][BOXK] as the TMA boxes arrive (token slots past M and k past
 // K are zeros there).
 template <int BITS, int MT, typename XT>
-__device__ __forceinline__ void convert_tile(const unsigned char *raw, uint4 *xs, int ctid) {
+__device__ __forceinline__ void convert_tile(const unsigned char *raw, uint4 *xs, int xtid) {
     using Geo = DecGeom<BITS>;
     constexpr int UNIT = Geo::UNIT, MTOK = MT * 8;
     const XT *src = reinterpret_cast<const XT *>(raw);
+    constexpr int XTHREADS = DecWarps<MT>::X * 32;
 #pragma unroll
-    for (int it = 0; it < (Geo::UPT * MTOK + DK_CTHREADS - 1) / DK_CTHREADS; ++it) {
-        const int idx = ctid + it * DK_CTHREADS;
-        if (idx >= Geo::UPT * MTOK) break;
+    for (int it = 0; it < Geo::UPT * MTOK / XTHREADS; ++it) {
+        const int idx = xtid + it * XTHREADS;
         const int m = idx / Geo::UPT, ud = idx % Geo::UPT;
         const int k = ud * UNIT;
         const XT *u = src + ((k / Geo::BOXK) * MTOK + m) * Geo::BOXK + (k % Geo::BOXK);
@@ -238,7 +243,7 @@ __device__ __forceinline__ int dec_cta_of(int64_t tile, int64_t tiles, int64_t c
 }
 
 template <int BITS, int MT>
-__global__ void __launch_bounds__(DK_THREADS, 1)
+__global__ void __launch_bounds__(DecWarps<MT>::THREADS, 1)
 qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap s_map,
                   const __grid_constant__ CUtensorMap z_map, const __grid_constant__ CUtensorMap x_map,
                   const DecParams p) {
@@ -278,7 +283,7 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     const int rb0 = (int)(t0 / p.KT), kt0 = (int)(t0 % p.KT);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, DK_CWARPS); mbar_init(xdone + s, DK_CWARPS); }
+        for (int s = 0; s < S; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, DK_CWARPS); mbar_init(xdone + s, DecWarps<MT>::X); }
         for (int b = 0; b < 2; ++b) { mbar_init(red_full + b, DK_CWARPS); mbar_init(red_free + b, 1); }
         mbar_init(cdone, (unsigned)(p.cluster > 1 ? (p.cluster - 1) * DK_HWARPS : 1));   // one arrival per peer hand-over warp
         flags[0] = 0;
@@ -310,18 +315,25 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                                 kt * Geo::TILE_K + b * Geo::BOXK, 0, full + s);
             };
             const int npro = nt < S ? nt : S;
+            const int early = npro < 2 ? npro : 2;
             int rb = rb0, kt = kt0;
-            // weights, scales and zero points do not depend on the preceding kernel: request
-            // them before waiting for it
-            for (int i = 0; i < npro; ++i) {
+            // Weights, scales and zero points do not depend on the preceding kernel: the first two
+            // tiles are requested before waiting for it.  (Not more: the activations can only be
+            // requested after the wait and would queue behind megabytes of weight traffic.)
+            for (int i = 0; i < early; ++i) {
                 load_weights(i, rb, kt);
                 if (++kt == p.KT) { kt = 0; ++rb; }
             }
             pdl_wait();   // the activations may be written by the preceding kernel
             int kx = kt0;
-            for (int i = 0; i < npro; ++i) {
+            for (int i = 0; i < early; ++i) {
                 load_x(i, kx);
                 if (++kx == p.KT) kx = 0;
+            }
+            for (int i = early; i < npro; ++i) {
+                load_weights(i, rb, kt);
+                load_x(i, kt);
+                if (++kt == p.KT) { kt = 0; ++rb; }
             }
             int s = 0;
             unsigned ph = 0;
@@ -333,7 +345,23 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                 if (++s == S) { s = 0; ph ^= 1u; }
             }
         }
-    } else if (warp >= DK_HANDOVER0) {
+    } else if (warp >= DK_CONVERTER0 && warp < DecWarps<MT>::HANDOVER0) {
+        // ---- converters: each tile's raw activations -> fp16 fragments, ahead of the consumers ----
+        const int xtid = threadIdx.x - DK_CONVERTER0 * 32;
+        int s = 0;
+        unsigned ph = 0;
+        for (int i = 0; i < nt; ++i) {
+            mbar_wait(full + s, ph, dead, 5);
+            const unsigned char *raw = rst + (size_t)s * p.raw_bytes;
+            uint4 *xw = reinterpret_cast<uint4 *>(xst + (size_t)s * XB);
+            if (p.x_dtype == BW_F16) convert_tile<BITS, MT, __half>(raw, xw, xtid);
+            else if (p.x_dtype == BW_BF16) convert_tile<BITS, MT, __nv_bfloat16>(raw, xw, xtid);
+            else convert_tile<BITS, MT, float>(raw, xw, xtid);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(xdone + s);
+            if (++s == S) { s = 0; ph ^= 1u; }
+        }
+    } else if (warp >= DecWarps<MT>::HANDOVER0) {
         // ---- hand-over warps: take the finished sums of each row-block share off the consumers'
         // hands: whole row blocks are stored, shares go to the scratch and the last CTA to
         // arrive for a row block sums them in CTA order ----
@@ -349,7 +377,7 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             }
         };
         pdl_wait();   // outputs, scratch and counters may still be in use by the preceding kernel
-        const int htid = threadIdx.x - DK_HANDOVER0 * 32;          // 0..DK_HTHREADS-1
+        const int htid = threadIdx.x - DecWarps<MT>::HANDOVER0 * 32;          // 0..DK_HTHREADS-1
         constexpr int V4 = RED / 4 / DK_HTHREADS;                      // float4 per thread: 2 / 4 / 8
         int rb = rb0, kt = kt0, f = 0;
         for (int i = 0; i < nt; ++f) {
@@ -512,32 +540,13 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[a][mt][e] = 0.0f;
 
-        auto convert_stage = [&](int st) {
-            const unsigned char *raw = rst + (size_t)st * p.raw_bytes;
-            uint4 *xw = reinterpret_cast<uint4 *>(xst + (size_t)st * XB);
-            if (p.x_dtype == BW_F16) convert_tile<BITS, MT, __half>(raw, xw, threadIdx.x);
-            else if (p.x_dtype == BW_BF16) convert_tile<BITS, MT, __nv_bfloat16>(raw, xw, threadIdx.x);
-            else convert_tile<BITS, MT, float>(raw, xw, threadIdx.x);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(xdone + st);
-        };
-
         int kt = kt0, f = 0;
         int s = 0;
         unsigned ph = 0;
-        mbar_wait(full, 0u, dead, 2);
-        convert_stage(0);
 
         for (int i = 0; i < nt; ++i) {
-            if (i + 1 < nt) {
-                // all consumers, one tile ahead: the next tile's raw activations -> fp16 fragments
-                int s1 = s + 1;
-                unsigned ph1 = ph;
-                if (s1 == S) { s1 = 0; ph1 ^= 1u; }
-                mbar_wait(full + s1, ph1, dead, 2);
-                convert_stage(s1);
-            }
-            mbar_wait(xdone + s, ph, dead, 6);              // every warp converted its part of this tile
+            mbar_wait(full + s, ph, dead, 2);               // packed words, scales, zero points
+            mbar_wait(xdone + s, ph, dead, 6);              // activations converted
             Dequant<BITS> dqa, dqb;
             {
                 const int gtile = ((kt * Geo::TILE_K) >> p.g_shift) & (DK_GBOX - 1);   // the tile's first group inside its box
@@ -772,7 +781,7 @@ int launch_dec(const DecMaps &maps, DecParams p, cudaStream_t st) {
         BW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
-    return launch_pdl(kern, dim3((unsigned)ctas), dim3(DK_THREADS), smem, p.cluster, st, maps.w, maps.s, maps.z, maps.x, p);
+    return launch_pdl(kern, dim3((unsigned)ctas), dim3(DecWarps<MT>::THREADS), smem, p.cluster, st, maps.w, maps.s, maps.z, maps.x, p);
 }
 
 template <int BITS>
