@@ -8,7 +8,10 @@
 // Shape of the computation ("swap-AB"): the MMA's M dimension (128 rows, one TMEM lane each)
 // holds 128 WEIGHT rows, its N dimension holds up to 256 TOKENS, so every dequantized weight is
 // used by up to 256 tokens of one CTA and the accumulator D^T[n, m] lives in 128 lanes x BN
-// fp32 columns of tensor memory.
+// fp32 columns of tensor memory.  The dequantized weights (the A operand) never touch shared
+// memory: each dequantization thread owns one weight row = one TMEM lane and writes its 64 fp16
+// of a k-stage into 32 columns of that lane with tcgen05.st; the MMAs read A from tensor
+// memory and only the activations (B) from shared memory.
 //
 // Warp roles in a CTA of 576 threads (one output tile of 128 weight rows x BN tokens, BN from
 // 16 to 256 by token count):
@@ -16,13 +19,14 @@
 //                the [BN tokens x 64 k] fp16 activation tile (128-byte swizzle) of each k-stage
 //                and -- for small token tiles -- of the [128 rows x 64 k] tile of packed words,
 //                in two independent shared-memory rings
-//   warp 1       allocates tensor memory; one elected lane issues tcgen05.mma (kind::f16,
-//                M=128, N=BN, K=16, four per stage) and commits stages / the accumulator
+//   warp 1       allocates tensor memory (accumulator + four A stages); one elected lane issues
+//                tcgen05.mma (kind::f16, A in TMEM, M=128, N=BN, K=16, four per stage) and
+//                commits stages / the accumulator
 //   warps 2..17  four groups of 128 dequantization threads (one per weight row; group g takes
 //                k-stages g, g+4, ...): fetch the row's packed words (register prefetch one
 //                own stage ahead for large tiles, the TMA ring for small ones), expand them to
-//                fp16 in natural k order and store them as the A operand in the canonical
-//                K-major 128-byte-swizzled layout; afterwards the same warps are the epilogue:
+//                fp16 in natural k order and store them as the A operand into their TMEM lane
+//                (tcgen05.st); afterwards the same warps are the epilogue:
 //                tcgen05.ld of their TMEM lane quadrant, fp16 rounding + bias, coalesced stores
 // Small problems split K over the CTAs of a thread-block cluster; the partial tiles are summed
 // through distributed shared memory.  Stages are handed over with mbarriers; every wait is
@@ -105,6 +109,26 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
     asm volatile(
         "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Same MMA with the A operand (128 rows x 16 k, two fp16 per 32-bit column, one row per lane) in
+// tensor memory: only the B operand is read from shared memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Each thread of the warp writes 32 consecutive 32-bit columns of its own TMEM lane.
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 // Arrives on the mbarrier once all tcgen05.mma issued so far by this thread have completed.
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
@@ -215,8 +239,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
     // 1024-byte alignment is required by the 128-byte swizzle pattern
     unsigned char *smem = tc_smem_raw + ((1024u - (smem_addr(tc_smem_raw) & 1023u)) & 1023u);
     const int bn = p.bn, NSX = p.x_stages, NSW = p.w_stages;
-    unsigned char *a_tiles = smem;                                        // [TC_STAGES][128][128 B]  fp16 weights
-    unsigned char *x_tiles = a_tiles + TC_STAGES * TC_BM * 128;           // [NSX][bn][128 B]         activations
+    unsigned char *x_tiles = smem;                                        // [NSX][bn][128 B]         activations
     unsigned char *w_tiles = x_tiles + (size_t)NSX * bn * 128;            // [NSW][128][WPS*4 B]      packed words
     uint64_t *bars = reinterpret_cast<uint64_t *>(w_tiles + (size_t)NSW * W_STAGE_BYTES);
     uint64_t *a_full = bars, *a_empty = bars + TC_STAGES, *x_full = bars + 2 * TC_STAGES;
@@ -231,7 +254,11 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
     const int kt0 = blockIdx.z * p.kper;
     const int kt1 = min(kt0 + p.kper, p.k_stages);
     const int nk = max(kt1 - kt0, 0);
-    const uint32_t tmem_cols = bn < 32 ? 32u : (uint32_t)bn;
+    // tensor memory: the accumulator (bn columns) followed by TC_STAGES tiles of dequantized
+    // weights (the A operand: 128 lanes x 32 columns = 128 rows x 64 fp16 each)
+    const uint32_t acc_cols = bn < 32 ? 32u : (uint32_t)bn;
+    uint32_t tmem_cols = 32;
+    while (tmem_cols < acc_cols + TC_STAGES * (TC_BK / 2)) tmem_cols *= 2;
 
     if (tid == 0) {
         for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&a_full[s], 4); mbar_init(&a_empty[s], 1); }   // a_full: the four warps of one group
@@ -297,12 +324,12 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
                      mbar_wait(&x_full[si], phx, abort_flag, 3);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_addr = smem_addr(a_tiles + (size_t)sa * TC_BM * 128);
+                const uint32_t a_taddr = tmem_base + acc_cols + (uint32_t)sa * (TC_BK / 2);
                 const uint32_t b_addr = smem_addr(x_tiles + (size_t)si * bn * 128);
 #pragma unroll
                 for (int k4 = 0; k4 < TC_BK / 16; ++k4)
-                    umma_f16(tmem_base, umma_smem_desc(a_addr + k4 * 32), umma_smem_desc(b_addr + k4 * 32), idesc,
-                             (i | k4) != 0 ? 1u : 0u);
+                    umma_f16_ts(tmem_base, a_taddr + k4 * 8, umma_smem_desc(b_addr + k4 * 32), idesc,
+                                (i | k4) != 0 ? 1u : 0u);
                 umma_commit(&a_empty[sa]);     // both free once these MMAs have read their operands
                 umma_commit(&x_empty[si]);
                 if (++si == NSX) { si = 0; phx ^= 1u; }
@@ -378,10 +405,14 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
             expand_stage<BITS>(w, gc_now, kt * TC_BK, p.g_shift, (kt * TC_BK) >> p.g_shift, chunk);
             ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[sa], ((unsigned)(i / TC_STAGES) & 1u) ^ 1u, abort_flag, 4));
             if (!ok) break;
-            uint4 *arow = reinterpret_cast<uint4 *>(a_tiles + (size_t)sa * TC_BM * 128 + (size_t)row * 128);
+            {
+                // this thread's row of the A tile: 64 fp16 in k order = 32 columns of its TMEM lane
+                uint32_t a_regs[32];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) arow[c ^ (row & 7)] = chunk[c];
-            fence_proxy_async_smem();                    // generic-proxy stores -> visible to the tensor core
+                for (int c = 0; c < 8; ++c) { a_regs[4 * c] = chunk[c].x; a_regs[4 * c + 1] = chunk[c].y; a_regs[4 * c + 2] = chunk[c].z; a_regs[4 * c + 3] = chunk[c].w; }
+                tmem_st_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc_cols + (uint32_t)sa * (TC_BK / 2), a_regs);
+            }
+            tc_fence_before();                           // the stores are ordered before the arrival
             __syncwarp();
             if (lane == 0) mbar_arrive(&a_full[sa]);
             si += TC_DQ_GROUPS;
@@ -503,7 +534,7 @@ int launch_tc(const CUtensorMap &xmap, const CUtensorMap &wmap, TcParams p, cuda
     using SG = StageGeom<BITS>;
     auto kern = qmm_tc_kernel<BITS>;
     const size_t w_stage = (size_t)TC_BM * SG::WPS * 4, x_stage = (size_t)p.bn * 128;
-    const size_t fixed = (size_t)TC_STAGES * TC_BM * 128 + 1024 /*alignment slack*/ + 1024 /*barriers*/;
+    const size_t fixed = 1024 /*alignment slack*/ + 1024 /*barriers*/;
     // Packed-word ring: a multiple of the number of dequantization groups deep, so that each
     // group meets the phases of "its" barriers one after the other (a waiter that skipped a
     // phase could not tell phase k from phase k-2 by parity).
