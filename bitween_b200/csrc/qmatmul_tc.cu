@@ -46,10 +46,10 @@ namespace {
 
 constexpr int TC_BM = 128;        // weight rows per tile (MMA M)
 constexpr int TC_BK = 64;         // k per stage: 64 fp16 = one 128-byte swizzle row
-constexpr int TC_STAGES = 4;
+constexpr int TC_STAGES = 8;       // A-operand stages in tensor memory (8 x 32 columns next to a 256-column accumulator)
 constexpr int TC_DQ_GROUPS = 4;   // dequantization warp groups (4 warps each) taking alternate stages
 constexpr int TC_THREADS = 64 + TC_DQ_GROUPS * 128;
-static_assert(TC_STAGES == TC_DQ_GROUPS, "each dequantization group owns one A stage");
+static_assert(TC_STAGES % TC_DQ_GROUPS == 0, "each dequantization group owns whole A stages (phase parity)");
 constexpr unsigned TC_WAIT_LIMIT = 1u << 22;   // polls of >= 20 ns each: gives up after ~0.1-1 s
 
 __device__ int g_tc_status = 0;
@@ -200,17 +200,21 @@ template <int BITS> struct StageGeom {
 };
 
 // Expands the WPS words of one stage into the row's eight 16-byte chunks (8 consecutive k each).
-template <int BITS>
+// ONE: the whole stage lies in one quantization group (group_size >= 64): no per-word lookup.
+template <int BITS, bool ONE>
 __device__ __forceinline__ void expand_stage(const uint32_t (&w)[StageGeom<BITS>::WPS], const GroupConst (&gc)[4],
                                              int kbase, int g_shift, int grp0, uint4 (&chunk)[8]) {
     constexpr int VPI = 32 / BITS;
     constexpr int WPS = StageGeom<BITS>::WPS;
     Dequant<BITS> dq;
     int cur = -1;
+    if constexpr (ONE) dq.set(gc[0]);
 #pragma unroll
     for (int j = 0; j < WPS; ++j) {
-        const int gl = min(((kbase + j * VPI) >> g_shift) - grp0, 3);
-        if (gl != cur) { dq.set(gc[gl]); cur = gl; }
+        if constexpr (!ONE) {
+            const int gl = min(((kbase + j * VPI) >> g_shift) - grp0, 3);
+            if (gl != cur) { dq.set(gc[gl]); cur = gl; }
+        }
         if constexpr (BITS == 4) {
             uint32_t p[4];
             dq.run(w[j], p);                          // (c0,c4) (c1,c5) (c2,c6) (c3,c7)
@@ -314,7 +318,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
     } else if (warp == 1) {
         // ---- MMA issuer ----
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_f16(bn, p.x_is_bf16);
+            const uint32_t idesc = umma_idesc_f16(bn, 0);
             bool ok = true;
             int si = 0;
             unsigned phx = 0;
@@ -402,7 +406,8 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
                 if (lane == 0) mbar_arrive(&w_empty[si]);    // the packed words are in registers now
             }
             uint4 chunk[8];
-            expand_stage<BITS>(w, gc_now, kt * TC_BK, p.g_shift, (kt * TC_BK) >> p.g_shift, chunk);
+            if (gps == 1) expand_stage<BITS, true>(w, gc_now, kt * TC_BK, p.g_shift, (kt * TC_BK) >> p.g_shift, chunk);
+            else expand_stage<BITS, false>(w, gc_now, kt * TC_BK, p.g_shift, (kt * TC_BK) >> p.g_shift, chunk);
             ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[sa], ((unsigned)(i / TC_STAGES) & 1u) ^ 1u, abort_flag, 4));
             if (!ok) break;
             {
@@ -651,7 +656,7 @@ int qmatmul_tc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
     p.words_per_row = (int)(K / (32 / bits));
     p.k_stages = (int)((K + TC_BK - 1) / TC_BK);
     p.bn = M > 128 ? 256 : (M > 64 ? 128 : (M > 32 ? 64 : (M > 16 ? 32 : 16)));
-    p.x_is_bf16 = (direct && x_dtype == BW_BF16) ? 1 : 0;
+    p.x_is_bf16 = 0;
 
     CUtensorMap map;
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
