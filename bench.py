@@ -270,19 +270,32 @@ def run_decode8b(args, torch, dist, rank, world, device):
         ms_e2e = float(t.item())
     e2e_val = bytes_per_step * e2e_steps * world / (ms_e2e * 1e-3) / 1e9
 
-    # ---- per-shape breakdown (M = 1 and 16), each launch on weights that are not in L2 ----
+    # ---- per-shape breakdown (M = 1 and 16): the layer copies of one shape replayed as one graph,
+    # L2 flushed before every replay ----
     breakdown = {}
     if rank == 0:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
         for si, (name, N, K) in enumerate(LLAMA8B_SHAPES):
             for M in (1, 16):
                 def one():
                     for stack in layers:
                         L = stack[si]
                         quantized_matmul_cuda(xs[M][K], L.q, L.scale, L.zp, None, bits, g, out=outs[M][N])
+                one()
+                torch.cuda.synchronize()
+                run_one = one
+                if args.graph:
+                    g1 = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g1):
+                        one()
+                    run_one = g1.replay
                 for _ in range(3):
-                    one()
-                reps = 5
-                t_ms = time_region(torch, lambda: [one() for _ in range(reps)]) / (reps * args.layers)
+                    run_one()
+                reps, t_ms = 10, 0.0
+                for _ in range(reps):
+                    flush.fill_(1)                      # 256 MB written: evicts the layer copies from L2
+                    t_ms += time_region(torch, run_one)
+                t_ms /= reps * args.layers
                 breakdown[f"{name}_{N}x{K}_M{M}"] = {
                     "us": round(t_ms * 1e3, 2),
                     "GBps": round(decode_bytes(M, N, K, bits, g) / (t_ms * 1e-3) / 1e9, 1)}
@@ -297,6 +310,11 @@ def run_decode8b(args, torch, dist, rank, world, device):
                     "steps": e2e_steps},
             "bytes_per_launch": bytes_per_step / calls_per_step, "launches_per_step": launches_per_step,
             "breakdown": breakdown, "extra": extra, "kernel": decode_kernel,
+            # DRAM bytes of one launch from the committed ncu capture of the 14336x4096 M=1 launch
+            # (31.27 MB read + 0 written against 31.23 MB algorithmic), scaled to the average launch
+            "traffic": bytes_per_step / calls_per_step * (31.27 / 31.23),
+            "traffic_source": "ncu capture profiles/qmm_decode_kernel_14336x4096_w4g128.md: dram bytes = 1.001 x "
+                              "algorithmic bytes, scaled to the average launch of the sweep",
             "config": {"workload": "decode8b", "shapes": "Llama-3-8B linears x M{1,2,4,8,16}",
                        "bits": bits, "group_size": g, "layer_copies": args.layers,
                        "l2_policy": f"inputs larger than L2: {args.layers} distinct copies of every layer "
@@ -400,6 +418,7 @@ def main():
                 "roofline": {"bound": "hbm", "kernel": res["kernel"], "achieved": achieved,
                              "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                              "peak_source": peaks["source"], "traffic": res.get("traffic"),
+                             "traffic_source": res.get("traffic_source"),
                              "us_per_launch": ms_per_launch * 1e3,
                              "algorithmic_bytes_per_launch": res["bytes_per_launch"]},
                 "breakdown": res.get("breakdown", {}), "extra": res.get("extra", {})}
