@@ -357,6 +357,7 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             if (p.x_dtype == BW_F16) convert_tile<BITS, MT, __half>(raw, xw, xtid);
             else if (p.x_dtype == BW_BF16) convert_tile<BITS, MT, __nv_bfloat16>(raw, xw, xtid);
             else convert_tile<BITS, MT, float>(raw, xw, xtid);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // reads of the raw tile before its refill by TMA
             __syncwarp();
             if (lane == 0) mbar_arrive(xdone + s);
             if (++s == S) { s = 0; ph ^= 1u; }
@@ -608,6 +609,8 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                     }
                 }
             }
+            // generic-proxy reads of the stage are ordered before the TMA write that refills it
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(empty + s);          // this warp is done with the stage
             if (++s == S) { s = 0; ph ^= 1u; }

@@ -110,11 +110,13 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
         "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// (Called by all lanes of the issuing warp; one elected lane issues.)
 // Same MMA with the A operand (128 rows x 16 k, two fp16 per 32-bit column, one row per lane) in
 // tensor memory: only the B operand is read from shared memory.
 __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+        "{\n .reg .pred p, q;\n setp.ne.b32 p, %4, 0;\n elect.sync _|q, 0xffffffff;\n"
+        " @q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // Each thread of the warp writes 32 consecutive 32-bit columns of its own TMEM lane.
@@ -130,9 +132,12 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
         : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
-// Arrives on the mbarrier once all tcgen05.mma issued so far by this thread have completed.
+// Arrives on the mbarrier once all tcgen05.mma issued so far by this warp's elected lane have
+// completed (called by all lanes of the issuing warp).
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+    asm volatile(
+        "{\n .reg .pred q;\n elect.sync _|q, 0xffffffff;\n"
+        " @q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}" ::"r"(smem_addr(bar)) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -317,29 +322,33 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
         }
     } else if (warp == 1) {
         // ---- MMA issuer ----
-        if (lane == 0) {
-            const uint32_t idesc = umma_idesc_f16(bn, 0);
-            bool ok = true;
-            int si = 0;
-            unsigned phx = 0;
-            for (int i = 0; i < nk && ok; ++i) {
-                const int sa = i % TC_STAGES;
-                ok = mbar_wait(&a_full[sa], (unsigned)(i / TC_STAGES) & 1u, abort_flag, 2) &&
-                     mbar_wait(&x_full[si], phx, abort_flag, 3);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t a_taddr = tmem_base + acc_cols + (uint32_t)sa * (TC_BK / 2);
-                const uint32_t b_addr = smem_addr(x_tiles + (size_t)si * bn * 128);
+        // The whole warp runs the loop and one elected lane issues each tcgen05 instruction, so
+        // that addresses and descriptors are warp-uniform values: issued from a single divergent
+        // lane, every tcgen05.mma / tcgen05.commit took 80-90 cycles to issue (operands moved
+        // one by one into uniform registers) and the issuing thread, not the tensor pipe, set
+        // the pace of the kernel.
+        const uint32_t idesc = umma_idesc_f16(bn, 0);
+        bool ok = true;
+        int si = 0;
+        unsigned phx = 0;
+        for (int i = 0; i < nk && ok; ++i) {
+            const int sa = i % TC_STAGES;
+            const bool got = mbar_wait(&a_full[sa], (unsigned)(i / TC_STAGES) & 1u, abort_flag, 2) &&
+                             mbar_wait(&x_full[si], phx, abort_flag, 3);
+            ok = __all_sync(0xffffffffu, got);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_taddr = tmem_base + acc_cols + (uint32_t)sa * (TC_BK / 2);
+            const uint32_t b_addr = smem_addr(x_tiles + (size_t)si * bn * 128);
 #pragma unroll
-                for (int k4 = 0; k4 < TC_BK / 16; ++k4)
-                    umma_f16_ts(tmem_base, a_taddr + k4 * 8, umma_smem_desc(b_addr + k4 * 32), idesc,
-                                (i | k4) != 0 ? 1u : 0u);
-                umma_commit(&a_empty[sa]);     // both free once these MMAs have read their operands
-                umma_commit(&x_empty[si]);
-                if (++si == NSX) { si = 0; phx ^= 1u; }
-            }
-            if (ok) umma_commit(acc_full);     // accumulator complete (arrives at once when nk == 0)
+            for (int k4 = 0; k4 < TC_BK / 16; ++k4)
+                umma_f16_ts(tmem_base, a_taddr + k4 * 8, umma_smem_desc(b_addr + k4 * 32), idesc,
+                            (i | k4) != 0 ? 1u : 0u);
+            umma_commit(&a_empty[sa]);     // both free once these MMAs have read their operands
+            umma_commit(&x_empty[si]);
+            if (++si == NSX) { si = 0; phx ^= 1u; }
         }
+        if (ok) umma_commit(acc_full);     // accumulator complete (arrives at once when nk == 0)
     } else {
         // ---- dequantization threads (one weight row each), then epilogue ----
         const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
@@ -402,6 +411,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
                     const uint4 t = src[v];
                     w[4 * v] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
                 }
+                // generic-proxy reads of the slot must be ordered before the async-proxy (TMA) write
+                // that refills it: without this fence random rows read the next stage's words
+                fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&w_empty[si]);    // the packed words are in registers now
             }
@@ -410,6 +422,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
             else expand_stage<BITS, false>(w, gc_now, kt * TC_BK, p.g_shift, (kt * TC_BK) >> p.g_shift, chunk);
             ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[sa], ((unsigned)(i / TC_STAGES) & 1u) ^ 1u, abort_flag, 4));
             if (!ok) break;
+            tc_fence_after();                            // the MMAs that read this stage come before the stores below
             {
                 // this thread's row of the A tile: 64 fp16 in k order = 32 columns of its TMEM lane
                 uint32_t a_regs[32];
@@ -549,7 +562,7 @@ int launch_tc(const CUtensorMap &xmap, const CUtensorMap &wmap, TcParams p, cuda
     int nsx = (int)((227 * 1024 - fixed - (size_t)nsw * w_stage) / x_stage);
     if (nsx > 16) nsx = 16;
     if (nsx < 2) return BW_ERR_UNSUPPORTED;
-    p.w_direct = p.bn >= 128 ? 1 : 0;
+    p.w_direct = 0;   // packed words always come through the TMA ring (direct loads measured 0-9 % slower)
     if (p.w_direct) nsw = TC_DQ_GROUPS;   // ring unused: keep it minimal
     nsx = (int)((227 * 1024 - fixed - (size_t)nsw * w_stage) / x_stage);
     if (nsx > 16) nsx = 16;

@@ -369,6 +369,8 @@ rtn_quantize_pack_stream_kernel(const T *__restrict__ w, int64_t total_chunks, i
                 for (int j = 0; j < V; ++j) v[l][j] = 0.0f;
             }
         }
+        // generic-proxy reads of the stage are ordered before the bulk copy that refills it
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();                                    // the whole CTA has read this stage
         if (tid == 0) issue(it + RTN_STAGES);
 #pragma unroll

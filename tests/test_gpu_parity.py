@@ -313,6 +313,29 @@ def test_prefill_full_size_shape_against_gpu_dequant_matmul(M, bits, g):
     assert float((acc - ref).abs().max()) <= 2e-5 * float(ref.abs().max())   # both sides accumulate in fp32
 
 
+@pytest.mark.parametrize("bits,g", [(8, 32), (4, 32), (2, 32), (4, 64)])
+def test_tensor_core_long_k_many_tiles_is_race_free(bits, g):
+    # 6 row tiles x 16 token tiles over 48 k-stages: the packed-word ring is refilled by TMA many
+    # times while other warps still expand earlier stages (a missing proxy fence between the
+    # generic reads of a ring slot and the TMA write that refills it once corrupted random rows
+    # here, differently on every run)
+    N, K, M = 768, 3072, 4096
+    gen = torch.Generator(device=DEV).manual_seed(bits * 100 + g)
+    w = (torch.randn(N, K, device=DEV, generator=gen) * 0.02).to(torch.bfloat16)
+    q, s_h, z_h = quantize_rtn_to_module_buffers(w, bits, g)
+    w_h = dequantize_rtn(q, s_h, z_h, g, bits=bits, out_dtype=torch.float16)
+    x = torch.randn(M, K, device=DEV, generator=gen).half()
+    ref = x.float() @ w_h.float().T
+    first = None
+    for _ in range(4):
+        acc = quantized_matmul_cuda(x, q, s_h, z_h, None, bits, g, out_dtype=torch.float32)
+        assert _lib.last_qmatmul_kernel() == "qmm_tc_kernel"
+        assert float((acc - ref).abs().max()) <= 2e-5 * float(ref.abs().max())
+        first = acc if first is None else first
+        assert torch.equal(acc, first)
+    assert _lib.lib().bw_device_status() == 0
+
+
 def test_forward_kernel_selection():
     q, s_h, z_h, b_h = _make_layer(5, 64, 256, 4, 128, False)
     x = torch.zeros(4, 256, dtype=torch.float16, device=DEV)
