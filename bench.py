@@ -322,25 +322,53 @@ def run_decode8b(args, torch, dist, rank, world, device):
                        "cuda_graph": bool(args.graph)}}
 
 
+def graph_ms(torch, body, flush=None, reps=5):
+    """CUDA-event time (ms) of one replay of `body` captured as a CUDA graph, L2 flushed before each replay."""
+    body()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        body()
+    g.replay()
+    total = 0.0
+    for _ in range(reps):
+        if flush is not None:
+            flush.fill_(1)
+        total += time_region(torch, g.replay)
+    return total / reps
+
+
 def run_extras(args, torch, fn, qmm, device, gen):
-    """RTN quantize+pack GB/s and prefill TFLOP/s on the same shapes (reported, not the headline)."""
+    """RTN quantize+pack GB/s, W8 g128 decode GB/s and prefill TFLOP/s on the same shapes (reported, not
+    the headline).  Every measurement replays a CUDA graph of launches on distinct layer copies with the
+    L2 flushed (256 MB written) before each replay."""
     out = {}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     # RTN: bf16 weights, fp32 arithmetic, fp32 scale + int32 zero-point out
     tot_b, tot_ms = 0, 0.0
     per = {}
     for (name, N, K) in LLAMA8B_SHAPES:
         ws = [(torch.randn(N, K, device=device, generator=gen) * 0.02).to(torch.bfloat16) for _ in range(3)]
-        for bits, g in ((4, 128),):
-            for w in ws[:2]:
-                fn._rtn_launch(w, bits, g, torch.float32, torch.int32, True)
-            ms = time_region(torch, lambda: [fn._rtn_launch(w, bits, g, torch.float32, torch.int32, True) for w in ws]) / len(ws)
-            b = rtn_bytes(N, K, bits, g, 2)
-            per[f"{name}_{N}x{K}"] = round(b / (ms * 1e-3) / 1e9, 1)
-            tot_b += b
-            tot_ms += ms
+        bits, g = 4, 128
+        ms = graph_ms(torch, lambda: [fn._rtn_launch(w, bits, g, torch.float32, torch.int32, True) for w in ws], flush) / len(ws)
+        b = rtn_bytes(N, K, bits, g, 2)
+        per[f"{name}_{N}x{K}"] = round(b / (ms * 1e-3) / 1e9, 1)
+        tot_b += b
+        tot_ms += ms
         del ws
     out["rtn_w4g128_bf16in_GBps"] = round(tot_b / (tot_ms * 1e-3) / 1e9, 1)
     out["rtn_per_shape_GBps"] = per
+    # W8 g128 decode (the second weight format of the decode configuration), M = 1 and 16
+    w8 = {}
+    for (name, N, K) in LLAMA8B_SHAPES:
+        layers = [Layer(N, K, 8, 128, device, gen, torch, fn) for _ in range(4)]
+        for M in (1, 16):
+            x = torch.randn(M, K, device=device, generator=gen).to(torch.bfloat16)
+            y = torch.empty(M, N, device=device, dtype=torch.float16)
+            ms = graph_ms(torch, lambda: [qmm(x, L.q, L.scale, L.zp, None, 8, 128, out=y) for L in layers], flush) / len(layers)
+            w8[f"{name}_{N}x{K}_M{M}"] = round(decode_bytes(M, N, K, 8, 128) / (ms * 1e-3) / 1e9, 1)
+        del layers
+    out["decode_w8g128_GBps"] = w8
     # prefill
     pf = {}
     for (name, N, K) in LLAMA8B_SHAPES:
@@ -348,8 +376,7 @@ def run_extras(args, torch, fn, qmm, device, gen):
         for M in (args.prefill_m,):
             x = torch.randn(M, K, device=device, generator=gen).to(torch.float16)
             y = torch.empty(M, N, device=device, dtype=torch.float16)
-            qmm(x, L.q, L.scale, L.zp, None, 4, 128, out=y)
-            ms = time_region(torch, lambda: [qmm(x, L.q, L.scale, L.zp, None, 4, 128, out=y) for _ in range(3)]) / 3
+            ms = graph_ms(torch, lambda: [qmm(x, L.q, L.scale, L.zp, None, 4, 128, out=y) for _ in range(3)], flush) / 3
             pf[f"{name}_{N}x{K}_M{M}"] = round(2.0 * M * N * K / (ms * 1e-3) / 1e12, 1)
         del L
     out["prefill_w4g128_TFLOPs"] = pf
