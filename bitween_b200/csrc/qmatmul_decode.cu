@@ -131,10 +131,18 @@ __device__ __forceinline__ void mbar_wait(uint64_t *bar, unsigned parity, volati
         }
     }
 }
+// The producer warp calls these two with all lanes and warp-uniform arguments; one elected lane
+// issues (a single divergent lane pays for moving every operand into uniform registers).
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1, uint64_t *bar) {
     asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        "{\n .reg .pred q;\n elect.sync _|q, 0xffffffff;\n"
+        " @q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n}"
         ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_elect(uint64_t *bar, unsigned bytes) {
+    asm volatile(
+        "{\n .reg .pred q;\n elect.sync _|q, 0xffffffff;\n"
+        " @q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n}" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void bulk_load(void *dst, const void *src, unsigned bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -145,9 +153,6 @@ __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 // shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
 __device__ __forceinline__ uint32_t remote_smem(const void *local, uint32_t rank) {
@@ -282,26 +287,37 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     const int nt = (int)(dec_first_tile(blockIdx.x + 1, p.tiles, ctas) - t0);
     const int rb0 = (int)(t0 / p.KT), kt0 = (int)(t0 % p.KT);
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, DK_CWARPS); mbar_init(xdone + s, DecWarps<MT>::X); }
+    if (threadIdx.x < S) {                       // one thread per stage initialises its barriers
+        mbar_init(full + threadIdx.x, 1);
+        mbar_init(empty + threadIdx.x, DK_CWARPS);
+        mbar_init(xdone + threadIdx.x, DecWarps<MT>::X);
+    }
+    if (threadIdx.x == 32) {
         for (int b = 0; b < 2; ++b) { mbar_init(red_full + b, DK_CWARPS); mbar_init(red_free + b, 1); }
         mbar_init(cdone, (unsigned)(p.cluster > 1 ? (p.cluster - 1) * DK_HWARPS : 1));   // one arrival per peer hand-over warp
         flags[0] = 0;
+    }
+    if (threadIdx.x < S || threadIdx.x == 32) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
-    if (p.cluster > 1) cluster_sync_all();   // every CTA's barriers exist before a peer arrives on them
+    // Every CTA's barriers must exist before a peer arrives on them: all threads arrive on the cluster
+    // barrier here; only the hand-over warps, the only ones that touch a peer, wait for it (later).
+    if (p.cluster > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 
     if (warp == DK_PRODUCER) {
-        // ---- producer: one lane feeds the ring ----
-        if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&w_map) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&s_map) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&z_map) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&x_map) : "memory");
+        // ---- producer: the warp runs the loop, one elected lane issues each copy ----
+        {
+            if (lane == 0) {
+                asm volatile("prefetch.tensormap [%0];" ::"l"(&w_map) : "memory");
+                asm volatile("prefetch.tensormap [%0];" ::"l"(&s_map) : "memory");
+                asm volatile("prefetch.tensormap [%0];" ::"l"(&z_map) : "memory");
+                asm volatile("prefetch.tensormap [%0];" ::"l"(&x_map) : "memory");
+            }
+            __syncwarp();
             auto load_weights = [&](int s, int rb, int kt) {
-                mbar_expect_tx(full + s, stage_tx);
+                mbar_expect_tx_elect(full + s, stage_tx);
                 tma_load_2d(wst + (size_t)s * DK_W_BYTES, &w_map, kt * DK_WORDS, rb * DK_ROWS, full + s);
                 const int grp0 = ((kt * Geo::TILE_K) >> p.g_shift) & ~(DK_GBOX - 1);   // TMA boxes start on 16-byte boundaries
                 tma_load_2d(cst + (size_t)s * 2 * DK_C_BYTES, &s_map, grp0, rb * DK_ROWS, full + s);
@@ -378,6 +394,7 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             }
         };
         pdl_wait();   // outputs, scratch and counters may still be in use by the preceding kernel
+        if (p.cluster > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // the peers' barriers are initialised
         const int htid = threadIdx.x - DecWarps<MT>::HANDOVER0 * 32;          // 0..DK_HTHREADS-1
         constexpr int V4 = RED / 4 / DK_HTHREADS;                      // float4 per thread: 2 / 4 / 8
         int rb = rb0, kt = kt0, f = 0;
