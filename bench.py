@@ -1,19 +1,22 @@
 #!/usr/bin/env python3
 """Benchmark of the quantized hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode8b|tp70b]
 
 Headline metric: W4 g128 decode qmatmul throughput in GB/s of ALGORITHMIC bytes
 (packed weights + fp16 scale/zero-point + activations in + outputs out, per launch).
 
 Workloads
-  decode8b   (default at N=1) one step = one decode pass of M in {1,2,4,8,16} tokens over a
-             stack of Llama-3-8B-shaped W4 g128 linears (4096->4096, 4096->1024, 4096->14336,
+  decode8b   (default) one step = one decode pass of M in {1,2,4,8,16} tokens over a stack of
+             Llama-3-8B-shaped W4 g128 linears (4096->4096, 4096->1024, 4096->14336,
              14336->4096), `--layers` distinct copies of each so that every launch reads weights
-             that are not in L2 (the stack is several times the 126 MB L2).
-  tp70b      (default at N>1) one step = decode batch 64 through the seven W4 g128 linears of
-             Llama-3-70B-shaped decoder layers, tensor-parallel over N GPUs (column-parallel
-             q/k/v/gate/up, row-parallel o/down + NCCL all-reduce), strong scaling.
+             that are not in L2 (the stack is several times the 126 MB L2).  With N GPUs every
+             rank runs the step on its own layers (layers are independent: no collective on the
+             data path, weak scaling; value = bytes of all ranks / max-over-ranks time).
+  tp70b      one step = decode batch 64 through the seven W4 g128 linears of Llama-3-70B-shaped
+             decoder layers, tensor-parallel over N GPUs (column-parallel q/k/v/gate/up,
+             row-parallel o/down + NCCL all-reduce), strong scaling.  At N > 1 the default run
+             also executes it and reports it under extra.tp70b.
 Synthetic data: weights ~ N(0, 0.02) rounded to bf16 and RTN-quantized on the device by this
 library's own kernel; activations ~ N(0, 1) bf16.  No checkpoint or dataset is involved.
 
@@ -420,10 +423,26 @@ def main():
 
     workload = args.workload
     if workload == "auto":
-        workload = "decode8b" if world == 1 else "tp70b"
+        workload = "decode8b"
     if workload == "decode8b":
+        # The decode sweep shards over GPUs by layer: every rank streams its own layers, no
+        # collective on the data path (weak scaling).  With more than one GPU the tensor-parallel
+        # 70B-shaped workload (strong scaling, NCCL all-reduce after the row-parallel layers) runs
+        # afterwards and is reported under extra.tp70b.
         res = run_decode8b(args, torch, dist, rank, world, device)
         scaling = "weak"
+        if world > 1:
+            res["config"]["parallelism"] = f"dp{world}: each rank runs the sweep on its own layer copies, no collective"
+            if not args.no_extra:
+                import copy
+                from bitween_b200 import tp_bench
+                targs = copy.copy(args)
+                targs.steps = min(args.steps, 30)
+                tp = tp_bench.run_tp70b(targs, torch, dist, rank, world, device, ClockSampler, time_region, decode_bytes)
+                res.setdefault("extra", {})["tp70b"] = {
+                    "metric": "w4g128_qmatmul_decode_GBps", "value": tp["value"], "unit": "GB/s", "scaling": "strong",
+                    "ms_per_step": tp["ms"] / targs.steps, "steps": targs.steps, "kernel": tp["kernel"],
+                    "e2e": tp["e2e"], "config": tp["config"]}
     elif workload == "tp70b":
         from bitween_b200 import tp_bench
         res = tp_bench.run_tp70b(args, torch, dist, rank, world, device, ClockSampler, time_region, decode_bytes)
