@@ -190,7 +190,8 @@ struct TcParams {
     int k_stages;       // ceil(K / 64)
     int bn;             // tokens per tile: 16, 32, 64, 128 or 256
     int x_stages;       // depth of the TMA ring of activation tiles
-    int w_stages;       // depth of the TMA ring of packed-word tiles (a multiple of the dequant groups)
+    int w_stages;       // depth of the TMA ring of packed-word slots (a power of two)
+    int w_stages_log2;
     int splits;         // split-K factor = cluster size along grid z
     int kper;           // k-stages per split
     int x_is_bf16;      // always 0: kind::f16 MMAs take both operands in one 16-bit format
@@ -202,6 +203,7 @@ template <int BITS> struct StageGeom {
     static constexpr int VPI = 32 / BITS;             // codes per word
     static constexpr int WPS = TC_BK / VPI;           // words per row per stage: 4 / 8 / 16
     static constexpr int VPS = WPS / 4;               // 16-byte vectors per row per stage: 1 / 2 / 4
+    static constexpr int SPS = 32 / WPS;              // k-stages per 128-byte row segment of a packed-word slot: 8 / 4 / 2
 };
 
 // Expands the WPS words of one stage into the row's eight 16-byte chunks (8 consecutive k each).
@@ -243,13 +245,15 @@ template <int BITS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, const TcParams p) {
     using SG = StageGeom<BITS>;
-    constexpr int W_STAGE_BYTES = TC_BM * SG::WPS * 4;                    // packed words of 128 rows, one stage
+    // one slot of the packed-word ring: 128 rows x 128 bytes (SPS k-stages), 128-byte swizzle; whole
+    // 128-byte row segments keep the DRAM accesses of the weight stream efficient
+    constexpr int W_STAGE_BYTES = TC_BM * 128;
     extern __shared__ unsigned char tc_smem_raw[];
     // 1024-byte alignment is required by the 128-byte swizzle pattern
     unsigned char *smem = tc_smem_raw + ((1024u - (smem_addr(tc_smem_raw) & 1023u)) & 1023u);
     const int bn = p.bn, NSX = p.x_stages, NSW = p.w_stages;
     unsigned char *x_tiles = smem;                                        // [NSX][bn][128 B]         activations
-    unsigned char *w_tiles = x_tiles + (size_t)NSX * bn * 128;            // [NSW][128][WPS*4 B]      packed words
+    unsigned char *w_tiles = x_tiles + (size_t)NSX * bn * 128;            // [NSW][128][128 B]        packed words
     uint64_t *bars = reinterpret_cast<uint64_t *>(w_tiles + (size_t)NSW * W_STAGE_BYTES);
     uint64_t *a_full = bars, *a_empty = bars + TC_STAGES, *x_full = bars + 2 * TC_STAGES;
     uint64_t *x_empty = x_full + NSX, *w_full = x_empty + NSX, *w_empty = w_full + NSW, *acc_full = w_empty + NSW;
@@ -272,7 +276,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
     if (tid == 0) {
         for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&a_full[s], 4); mbar_init(&a_empty[s], 1); }   // a_full: the four warps of one group
         for (int s = 0; s < NSX; ++s) { mbar_init(&x_full[s], 1); mbar_init(&x_empty[s], 1); }
-        for (int s = 0; s < NSW; ++s) { mbar_init(&w_full[s], 1); mbar_init(&w_empty[s], 4); }   // w_empty: 4 reader warps
+        for (int s = 0; s < NSW; ++s) { mbar_init(&w_full[s], 1); mbar_init(&w_empty[s], SG::SPS * 4); }   // w_empty: 4 reader warps per k-stage of the slot
         mbar_init(acc_full, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -289,16 +293,17 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
         // (the small packed-word stages are freed by the dequantization warps as soon as they
         // have been read into registers, so this ring runs far ahead of the tensor core)
         if (lane == 0) {
-            int ix = 0, iw = p.w_direct ? nk : 0;   // large tiles read packed words with plain loads
+            const int nslots = (nk + SG::SPS - 1) / SG::SPS;   // packed-word slots of this CTA's k range
+            int ix = 0, iw = p.w_direct ? nslots : 0;
             int sx = 0, sw = 0;                     // ring slots and phases advance without divisions
             unsigned phx = 0, phw = 0, idle = 0;
-            while (ix < nk || iw < nk) {
+            while (ix < nk || iw < nslots) {
                 bool progressed = false;
-                if (iw < nk) {
+                if (iw < nslots) {
                     const int s = sw;
                     if (mbar_try_wait(&w_empty[s], phw ^ 1u)) {
                         mbar_expect_tx(&w_full[s], (unsigned)W_STAGE_BYTES);
-                        tma_load_2d(w_tiles + (size_t)s * W_STAGE_BYTES, &w_map, (kt0 + iw) * SG::WPS, n0, &w_full[s]);
+                        tma_load_2d(w_tiles + (size_t)s * W_STAGE_BYTES, &w_map, (kt0 + iw * SG::SPS) * SG::WPS, n0, &w_full[s]);
                         ++iw;
                         if (++sw == NSW) { sw = 0; phw ^= 1u; }
                         progressed = true;
@@ -390,8 +395,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
             if (p.w_direct) prefetch_words(kt0 + dgroup);
         }
         bool ok = true;
-        int si = dgroup;                                 // slot in the packed-word ring (NSW % groups == 0)
-        unsigned phw = 0;
+        const int swz = (row & 7);                       // 128-byte swizzle of the packed-word slots
         for (int i = dgroup; i < nk; i += TC_DQ_GROUPS) {
             const int sa = i % TC_STAGES;
             const int kt = kt0 + i;
@@ -403,19 +407,23 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
                 for (int v = 0; v < SG::VPS; ++v) { w[4 * v] = wv[v].x; w[4 * v + 1] = wv[v].y; w[4 * v + 2] = wv[v].z; w[4 * v + 3] = wv[v].w; }
                 if (i + TC_DQ_GROUPS < nk) prefetch_words(kt + TC_DQ_GROUPS);
             } else {
+                // stage i lies in slot i / SPS of this CTA, at position (i % SPS) of each 128-byte row
+                const int slot = i / SG::SPS, si = slot & (NSW - 1);
+                const unsigned phw = (unsigned)(slot >> p.w_stages_log2) & 1u;
                 ok = __all_sync(0xffffffffu, mbar_wait(&w_full[si], phw, abort_flag, 6));
                 if (!ok) break;
-                const uint4 *src = reinterpret_cast<const uint4 *>(w_tiles + (size_t)si * W_STAGE_BYTES + (size_t)row * SG::WPS * 4);
+                const uint4 *src = reinterpret_cast<const uint4 *>(w_tiles + (size_t)si * W_STAGE_BYTES + (size_t)row * 128);
+                const int c0 = (i % SG::SPS) * SG::VPS;
 #pragma unroll
                 for (int v = 0; v < SG::VPS; ++v) {
-                    const uint4 t = src[v];
+                    const uint4 t = src[(c0 + v) ^ swz];
                     w[4 * v] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
                 }
                 // generic-proxy reads of the slot must be ordered before the async-proxy (TMA) write
                 // that refills it: without this fence random rows read the next stage's words
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&w_empty[si]);    // the packed words are in registers now
+                if (lane == 0) mbar_arrive(&w_empty[slot & (NSW - 1)]);    // the packed words are in registers now
             }
             uint4 chunk[8];
             if (gps == 1) expand_stage<BITS, true>(w, gc_now, kt * TC_BK, p.g_shift, (kt * TC_BK) >> p.g_shift, chunk);
@@ -433,8 +441,6 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
             tc_fence_before();                           // the stores are ordered before the arrival
             __syncwarp();
             if (lane == 0) mbar_arrive(&a_full[sa]);
-            si += TC_DQ_GROUPS;
-            if (si >= NSW) { si -= NSW; phw ^= 1u; }
         }
         // ---- epilogue ----
         const bool acc_ok = __all_sync(0xffffffffu, ok && mbar_wait(acc_full, 0u, abort_flag, 5));
@@ -551,23 +557,21 @@ template <int BITS>
 int launch_tc(const CUtensorMap &xmap, const CUtensorMap &wmap, TcParams p, cudaStream_t st) {
     using SG = StageGeom<BITS>;
     auto kern = qmm_tc_kernel<BITS>;
-    const size_t w_stage = (size_t)TC_BM * SG::WPS * 4, x_stage = (size_t)p.bn * 128;
+    const size_t w_stage = (size_t)TC_BM * 128, x_stage = (size_t)p.bn * 128;
     const size_t fixed = 1024 /*alignment slack*/ + 1024 /*barriers*/;
-    // Packed-word ring: a multiple of the number of dequantization groups deep, so that each
-    // group meets the phases of "its" barriers one after the other (a waiter that skipped a
-    // phase could not tell phase k from phase k-2 by parity).
-    int nsw = (int)(((p.bn >= 128 ? 32 : 64) * 1024) / w_stage);
-    nsw -= nsw % TC_DQ_GROUPS;
-    if (nsw < TC_DQ_GROUPS) nsw = TC_DQ_GROUPS;
+    // Packed-word ring: 4 slots of 16 KB for small token tiles (the weight stream is what is being
+    // waited for), 2 for large ones.  Each slot is always read by the same dequantization groups,
+    // once per phase (a waiter that skipped a phase could not tell phase k from phase k-2).
+    int nsw = p.bn >= 128 ? 2 : 4;
     int nsx = (int)((227 * 1024 - fixed - (size_t)nsw * w_stage) / x_stage);
     if (nsx > 16) nsx = 16;
     if (nsx < 2) return BW_ERR_UNSUPPORTED;
     p.w_direct = 0;   // packed words always come through the TMA ring (direct loads measured 0-9 % slower)
-    if (p.w_direct) nsw = TC_DQ_GROUPS;   // ring unused: keep it minimal
     nsx = (int)((227 * 1024 - fixed - (size_t)nsw * w_stage) / x_stage);
     if (nsx > 16) nsx = 16;
     p.x_stages = nsx;
     p.w_stages = nsw;
+    p.w_stages_log2 = nsw == 4 ? 2 : 1;
     // split-K (cluster along z) only for small tiles that would leave most SMs idle
     const int64_t tiles = ((p.N + TC_BM - 1) / TC_BM) * ((p.M + p.bn - 1) / p.bn);
     int splits = 1;
@@ -685,10 +689,10 @@ int qmatmul_tc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
     CUtensorMap wmap;
     const cuuint64_t wdims[2] = {(cuuint64_t)p.words_per_row, (cuuint64_t)N};
     const cuuint64_t wstrides[1] = {(cuuint64_t)p.words_per_row * 4};
-    const cuuint32_t wbox[2] = {(cuuint32_t)(TC_BK / (32 / bits)), (cuuint32_t)TC_BM};
+    const cuuint32_t wbox[2] = {32u, (cuuint32_t)TC_BM};   // 128 bytes of every row: 2, 4 or 8 k-stages
     const CUresult rw = encode_tiled_fn()(&wmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<int32_t *>(q), wdims,
                                           wstrides, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rw != CUDA_SUCCESS) return BW_ERR_UNSUPPORTED;
     set_last_kernel("qmm_tc_kernel");
