@@ -17,14 +17,15 @@
 // 16 to 256 by token count):
 //   warp 0       TMA producer (one lane): cp.async.bulk.tensor loads, without multicast, of
 //                the [BN tokens x 64 k] fp16 activation tile (128-byte swizzle) of each k-stage
-//                and -- for small token tiles -- of the [128 rows x 64 k] tile of packed words,
-//                in two independent shared-memory rings
-//   warp 1       allocates tensor memory (accumulator + four A stages); one elected lane issues
+//                and of packed-word slots [128 rows x 128 bytes] (2, 4 or 8 k-stages, 128-byte
+//                swizzle: whole 128-byte row segments keep the weight stream's DRAM accesses
+//                efficient), in two independent shared-memory rings
+//   warp 1       allocates tensor memory (accumulator + eight A stages); the whole warp runs the
+//                issue loop and one elected lane issues
 //                tcgen05.mma (kind::f16, A in TMEM, M=128, N=BN, K=16, four per stage) and
 //                commits stages / the accumulator
 //   warps 2..17  four groups of 128 dequantization threads (one per weight row; group g takes
-//                k-stages g, g+4, ...): fetch the row's packed words (register prefetch one
-//                own stage ahead for large tiles, the TMA ring for small ones), expand them to
+//                k-stages g, g+4, ...): fetch the row's packed words from the ring, expand them to
 //                fp16 in natural k order and store them as the A operand into their TMEM lane
 //                (tcgen05.st); afterwards the same warps are the epilogue:
 //                tcgen05.ld of their TMEM lane quadrant, fp16 rounding + bias, coalesced stores
