@@ -196,7 +196,6 @@ struct TcParams {
     int splits;         // split-K factor = cluster size along grid z
     int kper;           // k-stages per split
     int x_is_bf16;      // always 0: kind::f16 MMAs take both operands in one 16-bit format
-    int w_direct;       // packed words by plain loads (large tiles) instead of the TMA ring
 };
 
 // Words of one row for one 64-k stage, as 16-byte vectors, and the natural-order expansion.
@@ -295,7 +294,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
         // have been read into registers, so this ring runs far ahead of the tensor core)
         if (lane == 0) {
             const int nslots = (nk + SG::SPS - 1) / SG::SPS;   // packed-word slots of this CTA's k range
-            int ix = 0, iw = p.w_direct ? nslots : 0;
+            int ix = 0, iw = 0;
             int sx = 0, sw = 0;                     // ring slots and phases advance without divisions
             unsigned phx = 0, phw = 0, idle = 0;
             while (ix < nk || iw < nslots) {
@@ -380,21 +379,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
                 }
             }
         };
-        // Packed words: for large token tiles the MMA time per stage hides global-load latency, so
-        // each thread simply prefetches its row's next stage into registers (cheapest in
-        // instructions); for small tiles the words come through the deep TMA ring.
-        const uint4 *qrow = reinterpret_cast<const uint4 *>(p.q + n * p.words_per_row);
-        const int vec_per_row = p.words_per_row >> 2;
-        uint4 wv[SG::VPS];
-        auto prefetch_words = [&](int kt) {
-#pragma unroll
-            for (int v = 0; v < SG::VPS; ++v)
-                wv[v] = __ldg(qrow + min(kt * SG::VPS + v, vec_per_row - 1));   // past-the-end k meets zero activations
-        };
-        if (dgroup < nk) {
-            prefetch_consts(kt0 + dgroup);
-            if (p.w_direct) prefetch_words(kt0 + dgroup);
-        }
+        if (dgroup < nk) prefetch_consts(kt0 + dgroup);
         bool ok = true;
         const int swz = (row & 7);                       // 128-byte swizzle of the packed-word slots
         for (int i = dgroup; i < nk; i += TC_DQ_GROUPS) {
@@ -403,11 +388,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
             GroupConst gc_now[4] = {gcs[0], gcs[1], gcs[2], gcs[3]};
             if (i + TC_DQ_GROUPS < nk) prefetch_consts(kt + TC_DQ_GROUPS);
             uint32_t w[SG::WPS];
-            if (p.w_direct) {
-#pragma unroll
-                for (int v = 0; v < SG::VPS; ++v) { w[4 * v] = wv[v].x; w[4 * v + 1] = wv[v].y; w[4 * v + 2] = wv[v].z; w[4 * v + 3] = wv[v].w; }
-                if (i + TC_DQ_GROUPS < nk) prefetch_words(kt + TC_DQ_GROUPS);
-            } else {
+            {
                 // stage i lies in slot i / SPS of this CTA, at position (i % SPS) of each 128-byte row
                 const int slot = i / SG::SPS, si = slot & (NSW - 1);
                 const unsigned phw = (unsigned)(slot >> p.w_stages_log2) & 1u;
@@ -567,7 +548,6 @@ int launch_tc(const CUtensorMap &xmap, const CUtensorMap &wmap, TcParams p, cuda
     int nsx = (int)((227 * 1024 - fixed - (size_t)nsw * w_stage) / x_stage);
     if (nsx > 16) nsx = 16;
     if (nsx < 2) return BW_ERR_UNSUPPORTED;
-    p.w_direct = 0;   // packed words always come through the TMA ring (direct loads measured 0-9 % slower)
     nsx = (int)((227 * 1024 - fixed - (size_t)nsw * w_stage) / x_stage);
     if (nsx > 16) nsx = 16;
     p.x_stages = nsx;
