@@ -8,14 +8,15 @@
 //     [N/128] x [K-tiles] grid of weight tiles (128 rows x 128 bytes of packed words).  When there
 //     are fewer row blocks than SMs every row block gets the same number of CTAs; otherwise the
 //     tile list is cut into equal ranges ("stream-K");
-//   * warp 16 (one lane) keeps a deep shared-memory ring full with TMA, without multicast: per
+//   * warp 16 (one elected lane issues) keeps a shared-memory ring full with TMA, without multicast: per
 //     tile one 128-byte-swizzled box of packed words, one box each of the rows' scales and zero
 //     points (8 groups wide, so the box starts on a 16-byte boundary) and one box of the RAW
 //     activations of the tile's k range; completion on mbarriers, so no thread holds a load in
-//     flight.  Weights, scales and zero points are requested before griddepcontrol.wait, the
-//     activations after it (they may come from the preceding kernel);
-//   * warps 17.. (2 for up to 8 tokens, else 4) cast each tile's raw activations to fp16 (as bitween/modules.py:74) into
-//     tensor-core fragment order, pairing values the way the dequantizer pairs codes;
+//     flight.  The first two tiles' weights, scales and zero points are requested before
+//     griddepcontrol.wait, the activations after it (they may come from the preceding kernel);
+//   * warps 17.. (2 for up to 8 tokens, else 4) cast each tile's raw activations to fp16 (as
+//     bitween/modules.py:74) into tensor-core fragment order, pairing values the way the
+//     dequantizer pairs codes;
 //   * warps 0..15 (8 row slices x 2 chunk parities) are the consumers: each reads its part of
 //     the swizzled weight tile without bank conflicts, expands the codes with the exact
 //     magic-number dequantization and feeds mma.sync.m16n8k16 with the weights as the A operand
@@ -61,7 +62,7 @@ constexpr int DK_MAX_STAGES = 12;
 constexpr int DK_XBOX = 256;                       // widest TMA box of raw activations (elements)
 constexpr unsigned DK_WAIT_LIMIT = 1u << 22;       // polls of >= 20 ns each
 constexpr int DK_CNT_PER_WS = 4096;                // row-block counters per registered workspace
-constexpr int DK_CNT_WS = 16;                      // workspaces per device that can use the kernel at a time
+constexpr int DK_CNT_WS = 64;                      // workspaces per device that can use the kernel at a time
 
 __device__ int g_dec_status = 0;
 // Arrival counters of the row blocks.  atomicInc wraps them back to 0 when the last share of a

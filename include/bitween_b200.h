@@ -113,7 +113,9 @@ BW_API int bw_dequantize(const int32_t *qweight, const void *scale, int scale_dt
  *                   NULL when that is 0.  Calls that overlap on the GPU must not share it,
  *                   and a workspace address identifies the caller to the library (the
  *                   decode kernel keeps its row-block counters per workspace address, for
- *                   up to 16 addresses per device; further ones use the cluster kernel).
+ *                   up to 64 addresses per device; further ones use the cluster kernel).
+ *                   Make the first call with a new workspace address outside a stream
+ *                   capture (it looks up the address of the library's counter array).
  * Accumulation is fp32.  The kernel is chosen from M and the layout: up to 32 tokens run on
  * the persistent TMA-fed decode kernel (one launch; needs K/group_size to be a multiple of 8
  * and 16-byte aligned rows, else the cluster split-K streaming kernel runs), more on the
