@@ -256,7 +256,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
     unsigned char *w_tiles = x_tiles + (size_t)NSX * bn * 128;            // [NSW][128][128 B]        packed words
     uint64_t *bars = reinterpret_cast<uint64_t *>(w_tiles + (size_t)NSW * W_STAGE_BYTES);
     uint64_t *a_full = bars, *a_empty = bars + TC_STAGES, *x_full = bars + 2 * TC_STAGES;
-    uint64_t *x_empty = x_full + NSX, *w_full = x_empty + NSX, *w_empty = w_full + NSW, *acc_full = w_empty + NSW;
+    uint64_t *w_full = x_full + NSX, *w_empty = w_full + NSW, *acc_full = w_empty + NSW;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
@@ -275,7 +275,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
 
     if (tid == 0) {
         for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&a_full[s], 4); mbar_init(&a_empty[s], 1); }   // a_full: the four warps of one group
-        for (int s = 0; s < NSX; ++s) { mbar_init(&x_full[s], 1); mbar_init(&x_empty[s], 1); }
+        for (int s = 0; s < NSX; ++s) mbar_init(&x_full[s], 1);
         for (int s = 0; s < NSW; ++s) { mbar_init(&w_full[s], 1); mbar_init(&w_empty[s], SG::SPS * 4); }   // w_empty: 4 reader warps per k-stage of the slot
         mbar_init(acc_full, 1);
         *abort_flag = 0;
@@ -311,7 +311,10 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
                 }
                 if (ix < nk) {
                     const int s = sx;
-                    if (mbar_try_wait(&x_empty[s], phx ^ 1u)) {
+                    // the slot is free once the MMAs of stage ix - NSX have completed: that is the
+                    // commit that also frees the A stage of that k-stage (one commit per stage)
+                    const int jf = ix - NSX;
+                    if (jf < 0 || mbar_try_wait(&a_empty[jf % TC_STAGES], (unsigned)(jf / TC_STAGES) & 1u)) {
                         mbar_expect_tx(&x_full[s], (unsigned)bn * 128u);
                         tma_load_2d(x_tiles + (size_t)s * bn * 128, &x_map, (kt0 + ix) * TC_BK, m0, &x_full[s]);
                         ++ix;
@@ -349,8 +352,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
             for (int k4 = 0; k4 < TC_BK / 16; ++k4)
                 umma_f16_ts(tmem_base, a_taddr + k4 * 8, umma_smem_desc(b_addr + k4 * 32), idesc,
                             (i | k4) != 0 ? 1u : 0u);
-            umma_commit(&a_empty[sa]);     // both free once these MMAs have read their operands
-            umma_commit(&x_empty[si]);
+            umma_commit(&a_empty[sa]);     // the A stage and the activation slot are free once these MMAs have read them
             if (++si == NSX) { si = 0; phx ^= 1u; }
         }
         if (ok) umma_commit(acc_full);     // accumulator complete (arrives at once when nk == 0)
@@ -546,10 +548,8 @@ int launch_tc(const CUtensorMap &xmap, const CUtensorMap &wmap, TcParams p, cuda
     // once per phase (a waiter that skipped a phase could not tell phase k from phase k-2).
     int nsw = p.bn >= 128 ? 2 : 4;
     int nsx = (int)((227 * 1024 - fixed - (size_t)nsw * w_stage) / x_stage);
-    if (nsx > 16) nsx = 16;
+    if (nsx > TC_STAGES) nsx = TC_STAGES;   // activation slots are released by the commits of the A stages
     if (nsx < 2) return BW_ERR_UNSUPPORTED;
-    nsx = (int)((227 * 1024 - fixed - (size_t)nsw * w_stage) / x_stage);
-    if (nsx > 16) nsx = 16;
     p.x_stages = nsx;
     p.w_stages = nsw;
     p.w_stages_log2 = nsw == 4 ? 2 : 1;
