@@ -22,8 +22,9 @@
 //                efficient), in two independent shared-memory rings
 //   warp 1       allocates tensor memory (accumulator + eight A stages); the whole warp runs the
 //                issue loop and one elected lane issues
-//                tcgen05.mma (kind::f16, A in TMEM, M=128, N=BN, K=16, four per stage) and
-//                commits stages / the accumulator
+//                tcgen05.mma (kind::f16, A in TMEM, M=128, N=BN, K=16, four per stage) and one
+//                tcgen05.commit per stage (it frees the A stage for its dequantization group
+//                and the activation slot for the producer) / one for the accumulator
 //   warps 2..17  four groups of 128 dequantization threads (one per weight row; group g takes
 //                k-stages g, g+4, ...): fetch the row's packed words from the ring, expand them to
 //                fp16 in natural k order and store them as the A operand into their TMEM lane
