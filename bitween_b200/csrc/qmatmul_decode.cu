@@ -48,7 +48,6 @@ constexpr int DK_C_BYTES = DK_ROWS * DK_GBOX * 2;  // 2 KB per array per tile
 constexpr int DK_CWARPS = 16;                      // consumer warps
 constexpr int DK_HWARPS = 4;                       // hand-over warps (row-block sums -> outputs / scratch)
 constexpr int DK_HTHREADS = DK_HWARPS * 32;
-constexpr int DK_CTHREADS = DK_CWARPS * 32;
 // converter warps (raw activations -> fp16 fragments): 2 for one token tile, 4 for more
 template <int MT> struct DecWarps {
     static constexpr int X = MT == 1 ? 2 : 4;                       // converter warps
@@ -107,9 +106,6 @@ __device__ __forceinline__ void mbar_init(uint64_t *bar, unsigned count) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ bool mbar_test(uint64_t *bar, unsigned parity) {
     unsigned ok;
     asm volatile(
@@ -144,10 +140,6 @@ __device__ __forceinline__ void mbar_expect_tx_elect(uint64_t *bar, unsigned byt
     asm volatile(
         "{\n .reg .pred q;\n elect.sync _|q, 0xffffffff;\n"
         " @q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n}" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_load(void *dst, const void *src, unsigned bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
 }
 // ---- thread-block cluster helpers (row-block shares summed through distributed shared memory) ----
 __device__ __forceinline__ uint32_t cluster_rank() {
