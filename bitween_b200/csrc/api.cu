@@ -49,12 +49,11 @@ int qmatmul_decode(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, 
                    const __half *scale, const __half *zp, const __half *bias, void *out, int out_dtype,
                    int bits, int g, void *workspace, cudaStream_t st);
 int rtn_device_status();
-void set_rtn_stream(int on);
 long long div_self_check(unsigned long long n, unsigned long long seed);
 int qmatmul_grad_input(const void *go, int dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
                        const __half *scale, const __half *zp, void *gi, int bits, int g, cudaStream_t st);
 
-// Token counts above this go to the tensor-core GEMM, the rest to the streaming kernel.
+// Token counts above this go to the tensor-core GEMM, the rest to the streaming kernels.
 static int64_t g_tc_min_tokens = 32;
 #define TC_MIN_TOKENS g_tc_min_tokens
 
@@ -270,16 +269,15 @@ int bw_device_status(void) {
 int bw_version(void) { return 100; }
 const char *bw_last_qmatmul_kernel(void) { return g_last_kernel; }
 
-// Not in the public header: tuning hook used by the benchmark's sweep mode.
+#ifdef BW_TUNING
+// Tuning build only (-DBW_TUNING): process-wide, unsynchronised switches for kernel experiments.
 BW_API void bw_debug_set_smallm_tuning(int rt, int warps, int splits) { set_smallm_tuning(rt, warps, splits); }
 BW_API void bw_debug_set_pdl(int on) { set_smallm_pdl(on); }
 BW_API void bw_debug_set_decode(int enabled, int smem_kb, int max_ctas, int pdl) { set_decode_tuning(enabled, smem_kb, max_ctas, pdl); }
 BW_API void bw_debug_set_tc(int on) { set_tc_enabled(on); }
 BW_API void bw_debug_set_tc_splits(int s) { set_tc_splits(s); }
 BW_API void bw_debug_set_tc_min_tokens(int m) { g_tc_min_tokens = m; }
-BW_API void bw_debug_set_rtn_stream(int on) { set_rtn_stream(on); }
-// Test hook (allocates a counter; not for production callers): mismatches between the RTN
-// kernel's reciprocal-based division and IEEE division over n operand pairs.
-BW_API long long bw_debug_div_self_check(unsigned long long n, unsigned long long seed) { return div_self_check(n, seed); }
+#endif
+long long bw_selftest_division(unsigned long long n, unsigned long long seed) { return div_self_check(n, seed); }
 
 }  // extern "C"

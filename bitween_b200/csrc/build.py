@@ -23,6 +23,9 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
     "-I", os.path.join(ROOT, "include"), "-I", HERE,
 ]
+# BITWEEN_B200_TUNING=1 adds the experiment switches (bw_debug_*); the shipped build has none.
+if os.environ.get("BITWEEN_B200_TUNING") == "1":
+    NVCC_FLAGS.append("-DBW_TUNING")
 
 
 def _nvcc():

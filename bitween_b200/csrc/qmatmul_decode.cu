@@ -696,12 +696,20 @@ int sm_count() {
     return n;
 }
 
-// The slice of g_dec_cnt that calls with this workspace use.  Calls that may overlap on the GPU
-// already need distinct workspaces, so they also get distinct counters.  Returns nullptr when
-// all slices of the device are taken (the caller then uses another kernel).
+}  // namespace
+
+// The slice of g_dec_cnt that calls with this workspace use (shared by the decode and the
+// streaming kernel: calls on one workspace are ordered by their stream).  Calls that may
+// overlap on the GPU already need distinct workspaces, so they also get distinct counters.
+// Slices are handed out per workspace address; when all are taken the least recently used
+// one is reassigned (a call leaves its counters at zero, so a slice can change hands as long
+// as no kernel of its previous owner is still running -- that would take more than
+// DK_CNT_WS workspaces with work in flight on one device at a time).
 unsigned *counter_slice(const void *workspace) {
     static std::mutex mu;
     static const void *owner[64][DK_CNT_WS] = {};
+    static unsigned long long used[64][DK_CNT_WS] = {};
+    static unsigned long long tick = 0;
     static unsigned *base[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
@@ -711,15 +719,22 @@ unsigned *counter_slice(const void *workspace) {
         if (cudaGetSymbolAddress(&p, g_dec_cnt) != cudaSuccess) return nullptr;
         base[dev] = reinterpret_cast<unsigned *>(p);
     }
+    int pick = -1;
     for (int i = 0; i < DK_CNT_WS; ++i) {
-        if (owner[dev][i] == workspace) return base[dev] + (size_t)i * DK_CNT_PER_WS;
-        if (!owner[dev][i]) {
-            owner[dev][i] = workspace;
-            return base[dev] + (size_t)i * DK_CNT_PER_WS;
-        }
+        if (owner[dev][i] == workspace) { pick = i; break; }
+        if (!owner[dev][i]) { pick = i; break; }
     }
-    return nullptr;
+    if (pick < 0) {
+        pick = 0;
+        for (int i = 1; i < DK_CNT_WS; ++i)
+            if (used[dev][i] < used[dev][pick]) pick = i;
+    }
+    owner[dev][pick] = workspace;
+    used[dev][pick] = ++tick;
+    return base[dev] + (size_t)pick * DK_CNT_PER_WS;
 }
+
+namespace {
 
 inline int dec_token_tiles(int64_t M) { return M <= 8 ? 1 : (M <= 16 ? 2 : 4); }
 
@@ -848,8 +863,7 @@ size_t decode_workspace_bytes(int64_t M, int64_t N, int64_t K, int bits) {
     return (size_t)2 * DK_MAX_CTAS * dec_token_tiles(M) * 8 * DK_ROWS * sizeof(float);
 }
 
-// Returns BW_ERR_UNSUPPORTED (nothing launched) when no counter slice or no ring of two stages
-// is available; the caller then uses the cluster split-K kernel.
+// Returns BW_ERR_UNSUPPORTED (nothing launched) when no ring of two stages fits; the caller then uses the cluster split-K kernel.
 int qmatmul_decode(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
                    const __half *scale, const __half *zp, const __half *bias, void *out, int out_dtype,
                    int bits, int g, void *workspace, cudaStream_t st) {

@@ -439,8 +439,9 @@ rtn_quantize_pack_general_kernel(const T *__restrict__ w, int64_t num_spans, int
 }
 
 // The bulk-async variant is correct and tested but currently slower than the register-load
-// kernel (both are instruction-issue bound, about 30 instructions per weight), so it is opt-in.
-bool g_rtn_stream = false;
+// kernel (both are instruction-issue bound, about 30 instructions per weight), so it is opt-in
+// per call (BW_RTN_TMA_STREAM); the flag of the call in progress on this thread:
+thread_local bool t_rtn_stream = false;
 
 int64_t gcd64(int64_t a, int64_t b) { while (b) { int64_t t = a % b; a = b; b = t; } return a; }
 
@@ -463,7 +464,7 @@ int launch_typed(const T *w, int64_t N, int64_t K, int g, int32_t *q, ST *scale,
         const int64_t blocks = (warps + 7) / 8;
         if (blocks > 0x7fffffff) return BW_ERR_SHAPE;
         const int64_t tiles = (chunks + RTN_TILE_CHUNKS - 1) / RTN_TILE_CHUNKS;
-        if (g_rtn_stream && tiles >= 148 * 4) {
+        if (t_rtn_stream && tiles >= 148 * 4) {
             auto kern = rtn_quantize_pack_stream_kernel<T, NATIVE, BITS, ST, ZT>;
             const size_t smem = (size_t)RTN_STAGES * RTN_TILE_CHUNKS * 16 + RTN_STAGES * sizeof(uint64_t);
             BW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -557,12 +558,12 @@ int rtn_device_status() {
     if (v) (void)cudaMemcpyToSymbol(g_rtn_status, &zero, sizeof(int));
     return v;
 }
-void set_rtn_stream(int on) { g_rtn_stream = on != 0; }
 
 int rtn_quantize_pack(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int g,
                       int32_t *q, void *scale, int scale_dtype, void *zp, int zp_dtype,
                       unsigned flags, cudaStream_t st) {
     const bool native = !(flags & BW_RTN_UPCAST_F32);
+    t_rtn_stream = (flags & BW_RTN_TMA_STREAM) != 0;
     switch (w_dtype) {
         case BW_F32:
             return launch_scale<float, false>((const float *)w, N, K, bits, g, q, scale, scale_dtype, zp, zp_dtype, 1e-8f, st);

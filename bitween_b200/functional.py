@@ -21,7 +21,7 @@ def _compute_device(t):
     return torch.device("cuda", torch.cuda.current_device())
 
 
-def _rtn_launch(weight, bits, group_size, scale_dtype, zp_dtype, upcast):
+def _rtn_launch(weight, bits, group_size, scale_dtype, zp_dtype, upcast, flags=0):
     """weight: contiguous CUDA [N,K] float tensor.  Returns (q, scale, zp) on that device."""
     N, K = weight.shape
     vpi = 32 // bits
@@ -34,7 +34,7 @@ def _rtn_launch(weight, bits, group_size, scale_dtype, zp_dtype, upcast):
         rc = L.bw_rtn_quantize_pack(_lib.ptr(weight), _lib.dtype_code(weight.dtype), N, K, bits, group_size,
                                     _lib.ptr(q), _lib.ptr(scale), _lib.dtype_code(scale_dtype),
                                     _lib.ptr(zp), _lib.dtype_code(zp_dtype),
-                                    _lib.RTN_UPCAST_F32 if upcast else 0, _lib.stream_ptr(weight.device))
+                                    (_lib.RTN_UPCAST_F32 if upcast else 0) | flags, _lib.stream_ptr(weight.device))
     _lib.check(rc)
     return q, scale, zp
 

@@ -12,12 +12,12 @@ import torch
 
 F32, F16, BF16, I32 = 0, 1, 2, 3
 RTN_UPCAST_F32 = 1
+RTN_TMA_STREAM = 2
 
 _DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int32: I32}
 
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-# BITWEEN_B200_LIB points at an alternative build of the same library (kernel experiments).
-LIB_PATH = os.environ.get("BITWEEN_B200_LIB") or os.path.join(_PKG, "_C", "libbitween_b200.so")
+LIB_PATH = os.path.join(_PKG, "_C", "libbitween_b200.so")
 
 _lib = None
 _lock = threading.Lock()
@@ -65,36 +65,10 @@ def _declare(L):
     L.bw_last_qmatmul_kernel.restype = ctypes.c_char_p
     L.bw_version.argtypes = []
     L.bw_version.restype = i32
-    if hasattr(L, "bw_debug_set_smallm_tuning"):
-        L.bw_debug_set_smallm_tuning.argtypes = [i32, i32, i32]
-    if hasattr(L, "bw_debug_set_smallm_tuning"):
-        L.bw_debug_set_smallm_tuning.restype = None
     L.bw_device_status.argtypes = []
     L.bw_device_status.restype = i32
-    if hasattr(L, "bw_debug_set_rtn_stream"):
-        L.bw_debug_set_rtn_stream.argtypes = [i32]
-    if hasattr(L, "bw_debug_set_rtn_stream"):
-        L.bw_debug_set_rtn_stream.restype = None
-    if hasattr(L, "bw_debug_div_self_check"):
-        L.bw_debug_div_self_check.argtypes = [ctypes.c_ulonglong, ctypes.c_ulonglong]
-    if hasattr(L, "bw_debug_div_self_check"):
-        L.bw_debug_div_self_check.restype = ctypes.c_longlong
-    if hasattr(L, "bw_debug_set_tc_splits"):
-        L.bw_debug_set_tc_splits.argtypes = [i32]
-    if hasattr(L, "bw_debug_set_tc_splits"):
-        L.bw_debug_set_tc_splits.restype = None
-    if hasattr(L, "bw_debug_set_tc_min_tokens"):
-        L.bw_debug_set_tc_min_tokens.argtypes = [i32]
-    if hasattr(L, "bw_debug_set_tc_min_tokens"):
-        L.bw_debug_set_tc_min_tokens.restype = None
-    if hasattr(L, "bw_debug_set_tc"):
-        L.bw_debug_set_tc.argtypes = [i32]
-    if hasattr(L, "bw_debug_set_tc"):
-        L.bw_debug_set_tc.restype = None
-    if hasattr(L, "bw_debug_set_pdl"):
-        L.bw_debug_set_pdl.argtypes = [i32]
-    if hasattr(L, "bw_debug_set_pdl"):
-        L.bw_debug_set_pdl.restype = None
+    L.bw_selftest_division.argtypes = [ctypes.c_ulonglong, ctypes.c_ulonglong]
+    L.bw_selftest_division.restype = ctypes.c_longlong
 
 
 def lib():

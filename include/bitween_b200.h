@@ -59,6 +59,8 @@ typedef enum {
 #define BW_RTN_UPCAST_F32 1u /* 16-bit weights: up-cast each element to fp32 and do all
                                 arithmetic in fp32, i.e. what QuantizedLinear.from_float gets
                                 from `deepcopy(layer).to(float32)` (bitween/modules.py:191)   */
+#define BW_RTN_TMA_STREAM 2u /* large inputs: stream the weights through shared memory with bulk
+                                asynchronous copies instead of register loads; same results    */
 
 /*
  * RTN group-wise quantize + pack.  Replaces bitween/functional.py:3-45 (quantize_rtn): per
@@ -192,6 +194,15 @@ BW_API const char *bw_last_cuda_error(void);
 BW_API int bw_device_status(void);
 /* Library version: major*10000 + minor*100 + patch. */
 BW_API int bw_version(void);
+/*
+ * Self-test of the RTN kernel's division: it divides by one correctly rounded reciprocal per
+ * group plus FMA corrections instead of a hardware division (bitween/functional.py:25-29 divides).
+ * Runs both on n pseudo-random operand pairs (random and adversarial significands, the exponent
+ * range of the fast path, the Qmax divisors) and returns the number of results that differ
+ * from IEEE division in any bit (0 = exact), or -1 on a CUDA error.  Synchronous; allocates
+ * and frees an 8-byte counter.
+ */
+BW_API long long bw_selftest_division(unsigned long long n, unsigned long long seed);
 /* Name of the kernel the last bw_qmatmul call of this thread dispatched to (diagnostics). */
 BW_API const char *bw_last_qmatmul_kernel(void);
 

@@ -14,7 +14,7 @@ import pytest
 import torch
 
 from bitween_b200 import QuantizedLinear, dequantize_rtn, quantize_rtn, synth
-from bitween_b200.functional import quantize_rtn_to_module_buffers
+from bitween_b200.functional import _rtn_launch, quantize_rtn_to_module_buffers
 from bitween_b200.kernels import _lib
 from bitween_b200.kernels.cuda_loader import quantized_matmul_cuda, quantized_matmul_grad_input
 from helpers import ORACLE_DT, as_f32, assert_close_rms, from_bits, oracle_forward, rms, to_np
@@ -131,7 +131,7 @@ def test_rtn_division_by_reciprocal_is_correctly_rounded():
     # range of the fast path) the result must equal IEEE division bit for bit
     L = _lib.lib()
     for seed in (1, 2):
-        assert L.bw_debug_div_self_check(1 << 27, seed) == 0
+        assert L.bw_selftest_division(1 << 27, seed) == 0
 
 
 @pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
@@ -147,11 +147,7 @@ def test_rtn_streaming_kernel_equals_register_kernel(dt):
         w[11, 5] = float("inf")            # sends one group down the NaN/Inf-propagating path
     for bits, g in ((4, 128), (8, 32), (2, 64)):
         ref = quantize_rtn(w, bits=bits, group_size=g)
-        try:
-            L.bw_debug_set_rtn_stream(1)
-            got = quantize_rtn(w, bits=bits, group_size=g)
-        finally:
-            L.bw_debug_set_rtn_stream(0)
+        got = _rtn_launch(w, bits, g, w.dtype, torch.int32, upcast=False, flags=_lib.RTN_TMA_STREAM)
         assert L.bw_device_status() == 0
         for a, b in zip(got[:3], ref[:3]):
             assert _bits_equal(a, to_np(b)), (dt, bits, g)
