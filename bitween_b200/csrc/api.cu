@@ -22,6 +22,9 @@ void set_last_kernel(const char *name) { g_last_kernel = name; }
 int rtn_quantize_pack(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int g, int32_t *q,
                       void *scale, int scale_dtype, void *zp, int zp_dtype, unsigned flags,
                       cudaStream_t st);
+size_t rtn_batch_table_bytes(int njobs);
+int rtn_quantize_pack_batch(const bw_rtn_job *jobs, int njobs, int w_dtype, int bits, int g, int scale_dtype,
+                            int zp_dtype, unsigned flags, void *table_dev, cudaStream_t st);
 int dequantize(const int32_t *q, const void *scale, int scale_dtype, const void *zp, int zp_dtype,
                int64_t N, int64_t K, int bits, int g, void *out, int out_dtype, cudaStream_t st);
 int qmatmul_smallm(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
@@ -45,6 +48,9 @@ bool decode_path_ok(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K,
 size_t decode_workspace_bytes(int64_t M, int64_t N, int64_t K, int bits);
 int decode_device_status();
 void set_decode_tuning(int enabled, int smem_kb, int max_ctas, int pdl);
+#ifdef BW_TUNING
+void set_decode_trace(unsigned long long *buf);
+#endif
 int qmatmul_decode(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
                    const __half *scale, const __half *zp, const __half *bias, void *out, int out_dtype,
                    int bits, int g, void *workspace, cudaStream_t st);
@@ -79,6 +85,31 @@ int bw_rtn_quantize_pack(const void *w, int w_dtype, int64_t N, int64_t K, int b
         return BW_ERR_ALIGN;
     return rtn_quantize_pack(w, w_dtype, N, K, bits, group_size, qweight, scale, scale_dtype,
                              zero_point, zp_dtype, flags, (cudaStream_t)stream);
+}
+
+size_t bw_rtn_batch_table_bytes(int njobs) { return rtn_batch_table_bytes(njobs); }
+
+int bw_rtn_quantize_pack_batch(const bw_rtn_job *jobs, int njobs, int w_dtype, int bits, int group_size,
+                               int scale_dtype, int zp_dtype, unsigned flags, void *table_dev, size_t table_bytes,
+                               void *stream) {
+    if (njobs < 0) return BW_ERR_SHAPE;
+    if (njobs == 0) return BW_OK;
+    if (!jobs) return BW_ERR_NULL;
+    if (!is_float_dtype(w_dtype) || !is_float_dtype(scale_dtype)) return BW_ERR_DTYPE;
+    if (zp_dtype != BW_I32 && zp_dtype != BW_F16) return BW_ERR_DTYPE;
+    for (int j = 0; j < njobs; ++j) {
+        const bw_rtn_job &jb = jobs[j];
+        const int rc = check_quant_shape(jb.N, jb.K, bits, group_size);
+        if (rc != BW_OK) return rc;
+        if (jb.N * jb.K == 0) continue;
+        if (!jb.w || !jb.qweight || !jb.scale || !jb.zero_point) return BW_ERR_NULL;
+        if (!aligned_to(jb.w, dtype_size(w_dtype)) || !aligned_to(jb.qweight, 4) ||
+            !aligned_to(jb.scale, dtype_size(scale_dtype)) || !aligned_to(jb.zero_point, dtype_size(zp_dtype)))
+            return BW_ERR_ALIGN;
+    }
+    if (table_dev && (table_bytes < rtn_batch_table_bytes(njobs) || !aligned_to(table_dev, 8))) return BW_ERR_WORKSPACE;
+    return rtn_quantize_pack_batch(jobs, njobs, w_dtype, bits, group_size, scale_dtype, zp_dtype, flags, table_dev,
+                                   (cudaStream_t)stream);
 }
 
 int bw_dequantize(const int32_t *qweight, const void *scale, int scale_dtype, const void *zero_point,
@@ -121,13 +152,19 @@ size_t bw_qmatmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int bits, int
     return dec > base ? dec : base;
 }
 
-// `persistent_decode`: let M <= 32 run on the persistent TMA-fed decode kernel (needs the larger
-// workspace of bw_qmatmul_workspace_bytes); otherwise only the cluster split-K streaming kernel
-// and the tensor-core GEMM are used.
-static int qmatmul_dispatch(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *qweight,
+size_t bw_qmatmul_workspace_bytes_for(int64_t M, int64_t N, int64_t K, int bits, int group_size, int x_dtype, int x_align) {
+    const size_t all = bw_qmatmul_workspace_bytes(M, N, K, bits, group_size);
+    if (M <= TC_MIN_TOKENS || x_dtype != BW_F16 || x_align < 16) return all;
+    // more than 32 tokens of aligned fp16: the GEMM reads them in place; only layouts the GEMM
+    // cannot take need the streaming kernel's prepared activations
+    const size_t small = smallm_workspace_bytes(64, K, bits);
+    return small < all ? small : all;
+}
+
+// Argument checks shared by the qmatmul entry points (before any CUDA call).
+static int qmatmul_validate(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *qweight,
                             const void *scale, const void *zero_point, const void *bias, void *out, int out_dtype,
-                            int bits, int group_size, void *workspace, size_t workspace_bytes, void *stream,
-                            bool persistent_decode) {
+                            int bits, int group_size) {
     int rc = check_quant_shape(N, K, bits, group_size);
     if (rc != BW_OK) return rc;
     if (M < 0) return BW_ERR_SHAPE;
@@ -139,6 +176,20 @@ static int qmatmul_dispatch(const void *x, int x_dtype, int64_t M, int64_t N, in
         !aligned_to(qweight, 4) || !aligned_to(scale, 2) || !aligned_to(zero_point, 2) ||
         !aligned_to(bias, 2))
         return BW_ERR_ALIGN;
+    return BW_OK;
+}
+
+// `persistent_decode`: let M <= 32 run on the persistent TMA-fed decode kernel (needs the larger
+// workspace of bw_qmatmul_workspace_bytes); otherwise only the cluster split-K streaming kernel
+// and the tensor-core GEMM are used.  `allow_tc`: the tensor-core GEMM may be used (its
+// activation cast, where one is needed, fits the workspace).
+static int qmatmul_dispatch(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *qweight,
+                            const void *scale, const void *zero_point, const void *bias, void *out, int out_dtype,
+                            int bits, int group_size, void *workspace, size_t workspace_bytes, void *stream,
+                            bool persistent_decode, bool allow_tc) {
+    int rc = qmatmul_validate(x, x_dtype, M, N, K, qweight, scale, zero_point, bias, out, out_dtype, bits, group_size);
+    if (rc != BW_OK) return rc;
+    if (M == 0 || N == 0) return BW_OK;
     cudaStream_t st = (cudaStream_t)stream;
     const __half *s = (const __half *)scale, *z = (const __half *)zero_point, *b = (const __half *)bias;
     if (K == 0) {
@@ -153,11 +204,13 @@ static int qmatmul_dispatch(const void *x, int x_dtype, int64_t M, int64_t N, in
         rc = qmatmul_decode(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, workspace, st);
         if (rc != BW_ERR_UNSUPPORTED) return rc;   // otherwise nothing was launched: use the cluster split-K kernel
     }
-    if (!workspace || workspace_bytes < cluster_path_workspace_bytes(M, K, bits))
-        return BW_ERR_WORKSPACE;
-    if (M > TC_MIN_TOKENS && tc_path_ok(M, N, K, qweight, bits, group_size))
+    if (allow_tc && M > TC_MIN_TOKENS && tc_path_ok(M, N, K, qweight, bits, group_size)) {
+        const bool direct = x_dtype == BW_F16 && aligned_to(x, 16);   // TMA reads fp16 activations as they are
+        if (!direct && (!workspace || workspace_bytes < tc_workspace_bytes(M, K))) return BW_ERR_WORKSPACE;
         return qmatmul_tc(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, workspace, st);
+    }
     // token blocks of at most 64 through the streaming kernel
+    if (!workspace || workspace_bytes < smallm_workspace_bytes(M < 64 ? M : 64, K, bits)) return BW_ERR_WORKSPACE;
     const size_t xs = dtype_size(x_dtype), os = dtype_size(out_dtype);
     for (int64_t m0 = 0; m0 < M; m0 += 64) {
         const int64_t mc = (M - m0 < 64) ? (M - m0) : 64;
@@ -172,25 +225,41 @@ int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
                const void *scale, const void *zero_point, const void *bias, void *out, int out_dtype,
                int bits, int group_size, void *workspace, size_t workspace_bytes, void *stream) {
     return qmatmul_dispatch(x, x_dtype, M, N, K, qweight, scale, zero_point, bias, out, out_dtype, bits,
-                            group_size, workspace, workspace_bytes, stream, true);
+                            group_size, workspace, workspace_bytes, stream, true, true);
 }
 
 int bw_qmatmul_noalloc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K,
                        const int32_t *qweight, const void *scale, const void *zero_point,
                        const void *bias, void *out, int out_dtype, int bits, int group_size,
                        void *stream) {
-    int rc = check_quant_shape(N, K, bits, group_size);
+    int rc = qmatmul_validate(x, x_dtype, M, N, K, qweight, scale, zero_point, bias, out, out_dtype, bits, group_size);
     if (rc != BW_OK) return rc;
-    if (M < 0) return BW_ERR_SHAPE;
-    // reject requests whose prepared activations do not fit the built-in scratch before
-    // anything is launched
+    if (M == 0 || N == 0) return BW_OK;
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
     rc = noalloc_scratch(&scratch, &scratch_bytes);
     if (rc != BW_OK) return rc;
-    if (cluster_path_workspace_bytes(M, K, bits) > scratch_bytes) return BW_ERR_TOO_LARGE;
+    // What the kernel that will run really needs from the built-in scratch: nothing for the
+    // general kernel and for the tensor-core GEMM on 16-byte-aligned fp16 activations; M*K*2 bytes
+    // for the GEMM's fp16 cast of other activations -- when that does not fit, token blocks of 64
+    // go through the streaming kernel instead; the streaming kernel's prepared activations
+    // (K rounded up to a k-chunk x 8*ceil(min(M,64)/8) x 2 bytes) otherwise.  Requests that do not
+    // fit are refused before anything is launched.
+    bool allow_tc = true;
+    size_t need = 0;
+    if (K > 0 && smallm_fast_path_ok(x, x_dtype, K, qweight, bits, group_size)) {
+        const bool tc = M > TC_MIN_TOKENS && tc_path_ok(M, N, K, qweight, bits, group_size);
+        const bool direct = x_dtype == BW_F16 && aligned_to(x, 16);
+        if (tc && direct) need = 0;
+        else if (tc && tc_workspace_bytes(M, K) <= scratch_bytes) need = tc_workspace_bytes(M, K);
+        else {
+            allow_tc = false;
+            need = smallm_workspace_bytes(M < 64 ? M : 64, K, bits);
+        }
+    }
+    if (need > scratch_bytes) return BW_ERR_TOO_LARGE;
     return qmatmul_dispatch(x, x_dtype, M, N, K, qweight, scale, zero_point, bias, out, out_dtype, bits,
-                            group_size, scratch, scratch_bytes, stream, false);
+                            group_size, scratch, scratch_bytes, stream, false, allow_tc);
 }
 
 size_t bw_qmatmul_noalloc_max_scratch_bytes(void) {
@@ -253,7 +322,8 @@ const char *bw_status_string(int status) {
         case BW_ERR_TIMEOUT: return "a bounded device-side wait ran out";
         case BW_ERR_TOO_LARGE:
             return "request needs more scratch than the 2 MiB built into bw_qmatmul_noalloc "
-                   "(K rounded up to a k-chunk x 8*ceil(min(M,64)/8) x 2 bytes); use bw_qmatmul with a workspace";
+                   "(prepared activations of the streaming kernel: K rounded up to a k-chunk x 8*ceil(min(M,64)/8) x 2 bytes); "
+                   "use bw_qmatmul with a workspace";
         default: return "unknown status";
     }
 }
@@ -275,6 +345,7 @@ BW_API void bw_debug_set_smallm_tuning(int rt, int warps, int splits) { set_smal
 BW_API void bw_debug_set_pdl(int on) { set_smallm_pdl(on); }
 BW_API void bw_debug_set_decode(int enabled, int smem_kb, int max_ctas, int pdl) { set_decode_tuning(enabled, smem_kb, max_ctas, pdl); }
 BW_API void bw_debug_set_tc(int on) { set_tc_enabled(on); }
+BW_API void bw_debug_set_decode_trace(void *buf) { set_decode_trace((unsigned long long *)buf); }
 BW_API void bw_debug_set_tc_splits(int s) { set_tc_splits(s); }
 BW_API void bw_debug_set_tc_min_tokens(int m) { g_tc_min_tokens = m; }
 #endif

@@ -281,6 +281,60 @@ rtn_quantize_pack_kernel(const T *__restrict__ w, int64_t total_chunks, int cpg_
     }
 }
 
+// ---- several weight matrices in one launch ---------------------------------------------------
+// The per-layer loops of the callers (bitween/quantizer/quantizer.py:72-80,
+// bitween/gradual/base_wrapper.py:300-311) quantize one layer after the other; for the six or
+// seven linears of a decoder block the launches, not the kernel, are the cost.  Here a table in
+// device memory lists the matrices (all of one dtype, bit width and group size); every block
+// looks up the matrix its index falls into and then runs the single-matrix code on it.
+struct RtnBatchEntry {
+    const void *w;
+    int32_t *q;
+    void *scale;
+    void *zp;
+    long long chunks;        // 16-byte chunks of the matrix
+    long long first_block;   // first block index of the matrix in the batched grid
+};
+
+template <typename T, bool NATIVE, int BITS, int L, typename ST, typename ZT>
+__global__ void __launch_bounds__(256)
+rtn_quantize_pack_batch_kernel(const RtnBatchEntry *__restrict__ table, int njobs, int cpg_log2, float floor_s) {
+    constexpr int V = Elems16<T>::V;
+    __shared__ int job_s;
+    if (threadIdx.x == 0) {
+        int lo = 0, hi = njobs - 1;                      // last entry with first_block <= blockIdx.x
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (table[mid].first_block <= (long long)blockIdx.x) lo = mid; else hi = mid - 1;
+        }
+        job_s = lo;
+    }
+    __syncthreads();
+    const RtnBatchEntry e = table[job_s];
+    const T *w = reinterpret_cast<const T *>(e.w);
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (((int64_t)blockIdx.x - e.first_block) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t c0 = warp * (32 * L) + lane;
+    const int cpg = 1 << cpg_log2;
+    const uint32_t seg_mask = (cpg == 32) ? 0xffffffffu : (((1u << cpg) - 1u) << (lane & ~(cpg - 1)));
+    float v[L][V];
+#pragma unroll
+    for (int l = 0; l < L; ++l) {
+        const int64_t c = c0 + l * 32;
+        if (c < e.chunks) load16<T>(w + c * V, v[l]);
+        else {
+#pragma unroll
+            for (int j = 0; j < V; ++j) v[l][j] = 0.0f;
+        }
+    }
+#pragma unroll
+    for (int l = 0; l < L; ++l) {
+        const int64_t c = c0 + l * 32;
+        rtn_slot<T, NATIVE, BITS, ST, ZT>(v[l], c, c < e.chunks, lane, cpg, cpg_log2, seg_mask, floor_s, e.q,
+                                          reinterpret_cast<ST *>(e.scale), reinterpret_cast<ZT *>(e.zp));
+    }
+}
+
 // ---- streaming variant of the fast path: bulk-async copies into a shared-memory ring ------
 //
 // HBM latency under load on B200 is about 2 us, so ~100 KB per SM have to be in flight to
@@ -442,6 +496,9 @@ rtn_quantize_pack_general_kernel(const T *__restrict__ w, int64_t num_spans, int
 // kernel (both are instruction-issue bound, about 30 instructions per weight), so it is opt-in
 // per call (BW_RTN_TMA_STREAM); the flag of the call in progress on this thread:
 thread_local bool t_rtn_stream = false;
+// A batched call in progress on this thread: the device table, its length and the grid size.
+struct RtnBatchCall { const RtnBatchEntry *table; int njobs; long long blocks; };
+thread_local RtnBatchCall t_rtn_batch = {nullptr, 0, 0};
 
 int64_t gcd64(int64_t a, int64_t b) { while (b) { int64_t t = a % b; a = b; b = t; } return a; }
 
@@ -457,6 +514,13 @@ int launch_typed(const T *w, int64_t N, int64_t K, int g, int32_t *q, ST *scale,
     if (g % V == 0) {
         const int cpg = g / V;
         if (cpg <= 32 && (cpg & (cpg - 1)) == 0) { cpg_log2 = 0; while ((1 << cpg_log2) < cpg) ++cpg_log2; }
+    }
+    if (t_rtn_batch.njobs > 0) {
+        // (the caller has checked that every matrix of the batch takes the fast path)
+        if (cpg_log2 < 0) return BW_ERR_UNSUPPORTED;
+        rtn_quantize_pack_batch_kernel<T, NATIVE, BITS, L, ST, ZT><<<(unsigned)t_rtn_batch.blocks, 256, 0, st>>>(
+            t_rtn_batch.table, t_rtn_batch.njobs, cpg_log2, floor_s);
+        return check_launch("rtn_quantize_pack_batch_kernel");
     }
     if (cpg_log2 >= 0 && aligned_to(w, 16) && aligned_to(q, 8)) {
         const int64_t chunks = total / V;
@@ -577,6 +641,48 @@ int rtn_quantize_pack(const void *w, int w_dtype, int64_t N, int64_t K, int bits
         default:
             return BW_ERR_DTYPE;
     }
+}
+
+size_t rtn_batch_table_bytes(int njobs) { return njobs > 0 ? (size_t)njobs * sizeof(RtnBatchEntry) : 0; }
+
+// Quantizes `njobs` matrices with ONE kernel launch when all of them take the fast path (group a
+// power-of-two multiple of 16 bytes of weights, 16-byte aligned weights, 8-byte aligned packed
+// words), else one launch per matrix.  `table_dev` receives the job table (one asynchronous copy).
+int rtn_quantize_pack_batch(const bw_rtn_job *jobs, int njobs, int w_dtype, int bits, int g, int scale_dtype,
+                            int zp_dtype, unsigned flags, void *table_dev, cudaStream_t st) {
+    const int v = 16 / (int)dtype_size(w_dtype), lpt = w_dtype == BW_F32 ? 4 : 2;
+    bool fast = table_dev != nullptr && g % v == 0 && (g / v) <= 32 && ((g / v) & (g / v - 1)) == 0 && njobs <= 4096;
+    for (int j = 0; j < njobs && fast; ++j)
+        fast = aligned_to(jobs[j].w, 16) && aligned_to(jobs[j].qweight, 8);
+    if (!fast) {
+        for (int j = 0; j < njobs; ++j) {
+            if (jobs[j].N * jobs[j].K == 0) continue;
+            const int rc = rtn_quantize_pack(jobs[j].w, w_dtype, jobs[j].N, jobs[j].K, bits, g, jobs[j].qweight, jobs[j].scale,
+                                             scale_dtype, jobs[j].zero_point, zp_dtype, flags, st);
+            if (rc != BW_OK) return rc;
+        }
+        return BW_OK;
+    }
+    static thread_local RtnBatchEntry host_table[4096];
+    long long blocks = 0;
+    int used = 0, first = -1;
+    for (int j = 0; j < njobs; ++j) {
+        const long long chunks = (long long)(jobs[j].N * jobs[j].K) / v;
+        if (chunks == 0) continue;
+        if (first < 0) first = j;
+        host_table[used++] = {jobs[j].w, jobs[j].qweight, jobs[j].scale, jobs[j].zero_point, chunks, blocks};
+        const long long warps = (chunks + 32 * lpt - 1) / (32 * lpt);
+        blocks += (warps + 7) / 8;
+    }
+    if (used == 0) return BW_OK;
+    if (blocks > 0x7fffffff) return BW_ERR_SHAPE;
+    // (pageable source: the runtime stages the table before the call returns)
+    BW_CUDA_TRY(cudaMemcpyAsync(table_dev, host_table, (size_t)used * sizeof(RtnBatchEntry), cudaMemcpyHostToDevice, st));
+    t_rtn_batch = {reinterpret_cast<const RtnBatchEntry *>(table_dev), used, blocks};
+    const int rc = rtn_quantize_pack(jobs[first].w, w_dtype, jobs[first].N, jobs[first].K, bits, g, jobs[first].qweight,
+                                     jobs[first].scale, scale_dtype, jobs[first].zero_point, zp_dtype, flags, st);
+    t_rtn_batch = {nullptr, 0, 0};
+    return rc;
 }
 
 }  // namespace bw

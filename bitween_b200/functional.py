@@ -88,6 +88,47 @@ def quantize_rtn_to_module_buffers(weight: torch.Tensor, bits: int, group_size: 
 
 
 @torch.no_grad()
+def quantize_rtn_many_to_module_buffers(weights, bits: int, group_size: int):
+    """`quantize_rtn_to_module_buffers` for a list of weight matrices (the linears of a decoder
+    block, or of a whole model) with ONE kernel launch per (device, dtype) instead of one per
+    layer (C ABI: bw_rtn_quantize_pack_batch).  Returns a list of (qweight, scale, zero_point)
+    in the order of `weights`; every result equals the single-layer call's bit for bit."""
+    prepared = []
+    for weight in weights:
+        _validate(weight, bits, group_size)
+        if weight.dtype not in _FLOAT_DTYPES:
+            weight = weight.to(torch.float32)
+        prepared.append(weight.detach().to(_compute_device(weight)).contiguous())
+    results = [None] * len(prepared)
+    groups = {}
+    for i, w in enumerate(prepared):
+        groups.setdefault((w.device, w.dtype), []).append(i)
+    vpi = 32 // bits
+    L = _lib.lib()
+    for (device, dtype), idx in groups.items():
+        jobs = (_lib.RtnJob * len(idx))()
+        for j, i in enumerate(idx):
+            w = prepared[i]
+            N, K = w.shape
+            q = torch.empty((N, K // vpi), dtype=torch.int32, device=device)
+            s = torch.empty((N, K // group_size), dtype=torch.float16, device=device)
+            z = torch.empty((N, K // group_size), dtype=torch.float16, device=device)
+            results[i] = (q, s, z)
+            jobs[j] = _lib.RtnJob(w.data_ptr(), q.data_ptr(), s.data_ptr(), z.data_ptr(), N, K)
+        with torch.cuda.device(device):
+            nbytes = L.bw_rtn_batch_table_bytes(len(idx))
+            table = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=device)
+            rc = L.bw_rtn_quantize_pack_batch(jobs, len(idx), _lib.dtype_code(dtype), bits, group_size, _lib.F16, _lib.F16,
+                                              _lib.RTN_UPCAST_F32, _lib.ptr(table), table.numel(), _lib.stream_ptr(device))
+        _lib.check(rc)
+        # the kernel reads `table` and the weights asynchronously: keep them alive until it has run
+        table.record_stream(torch.cuda.current_stream(device))
+        for i in idx:
+            prepared[i].record_stream(torch.cuda.current_stream(device))
+    return results
+
+
+@torch.no_grad()
 def dequantize_rtn(q_packed: torch.Tensor, scale: torch.Tensor, zero_point: torch.Tensor, group_size: int,
                    bits: int = 8, out_dtype: torch.dtype = torch.float32):
     """Drop-in for bitween/functional.py:47-71: float32 [N, K] = scale * (code - zero_point).

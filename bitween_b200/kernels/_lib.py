@@ -38,14 +38,26 @@ def dtype_code(dt):
         raise TypeError(f"bitween_b200: unsupported dtype {dt}") from None
 
 
+class RtnJob(ctypes.Structure):
+    """bw_rtn_job of include/bitween_b200.h."""
+    _fields_ = [("w", ctypes.c_void_p), ("qweight", ctypes.c_void_p), ("scale", ctypes.c_void_p),
+                ("zero_point", ctypes.c_void_p), ("N", ctypes.c_int64), ("K", ctypes.c_int64)]
+
+
 def _declare(L):
     i64, i32, vp, u32, sz = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_uint, ctypes.c_size_t
     L.bw_rtn_quantize_pack.argtypes = [vp, i32, i64, i64, i32, i32, vp, vp, i32, vp, i32, u32, vp]
     L.bw_rtn_quantize_pack.restype = i32
+    L.bw_rtn_batch_table_bytes.argtypes = [i32]
+    L.bw_rtn_batch_table_bytes.restype = sz
+    L.bw_rtn_quantize_pack_batch.argtypes = [ctypes.POINTER(RtnJob), i32, i32, i32, i32, i32, i32, u32, vp, sz, vp]
+    L.bw_rtn_quantize_pack_batch.restype = i32
     L.bw_dequantize.argtypes = [vp, vp, i32, vp, i32, i64, i64, i32, i32, vp, i32, vp]
     L.bw_dequantize.restype = i32
     L.bw_qmatmul_workspace_bytes.argtypes = [i64, i64, i64, i32, i32]
     L.bw_qmatmul_workspace_bytes.restype = sz
+    L.bw_qmatmul_workspace_bytes_for.argtypes = [i64, i64, i64, i32, i32, i32, i32]
+    L.bw_qmatmul_workspace_bytes_for.restype = sz
     L.bw_qmatmul.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, vp, vp, i32, i32, i32, vp, sz, vp]
     L.bw_qmatmul.restype = i32
     L.bw_qmatmul_noalloc.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, vp, vp, i32, i32, i32, vp]

@@ -68,7 +68,8 @@ def quantized_matmul_cuda(x, qweight, scale, zero_point, bias, bits, group_size,
             raise ValueError("`out` must be a contiguous [M, N] tensor of out_dtype on x's device")
     L = _lib.lib()
     with torch.cuda.device(dev):
-        ws_bytes = L.bw_qmatmul_workspace_bytes(M, N, K, bits, group_size)
+        ws_bytes = L.bw_qmatmul_workspace_bytes_for(M, N, K, bits, group_size, _lib.dtype_code(x2.dtype),
+                                                    16 if x2.data_ptr() % 16 == 0 else 2)
         ws = _lib.workspace(dev, ws_bytes)
         rc = L.bw_qmatmul(_lib.ptr(x2), _lib.dtype_code(x2.dtype), M, N, K, _lib.ptr(qweight),
                           _lib.ptr(scale), _lib.ptr(zero_point), _lib.ptr(bias), _lib.ptr(out),
@@ -161,6 +162,13 @@ def quantized_matmul_noalloc(x, qweight, scale, zero_point, bias, bits, group_si
     M = x.numel() // K if K else 0
     if qweight.shape[1] * (32 // bits) != K or out.numel() != M * N:
         raise ValueError("shape mismatch between x, qweight and out")
+    if group_size < 1 or K % group_size != 0:
+        raise ValueError("Group size must be at least 1 and divide in_features.")
+    G = K // group_size
+    if tuple(scale.shape) != (N, G) or tuple(zero_point.shape) != (N, G):
+        raise ValueError(f"scale / zero_point must have shape {(N, G)}")
+    if bias is not None and bias.numel() != N:
+        raise ValueError("bias must have out_features elements")
     dev = x.device
     L = _lib.lib()
     with torch.cuda.device(dev):

@@ -77,14 +77,11 @@ class QuantizedLinear(nn.Module):
                                              self.bits, self.group_size, out_dtype)
 
     @classmethod
-    def from_float(cls, float_layer: nn.Linear, bits=8, group_size=32):
-        """RTN-quantize an nn.Linear.  Results are bit-identical to the reference's
-        `deepcopy(layer).to(float32)` -> `quantize_rtn` -> `.copy_()` casts (modules.py:189-213),
-        but the weight is read once in its own dtype by one kernel that writes the packed codes
-        and the fp16 scale / zero_point directly: no fp32 copy of the layer, no temporaries."""
-        weight = float_layer.weight.data
-        device = weight.device
-        qweight, scale, zero_point = quantize_rtn_to_module_buffers(weight, bits, group_size)
+    def from_buffers(cls, float_layer: nn.Linear, bits, group_size, qweight, scale, zero_point):
+        """A QuantizedLinear for `float_layer` around already computed RTN buffers (the results
+        of `quantize_rtn_to_module_buffers`, e.g. from the batched call or a cache).  The buffers
+        are adopted, not copied; the bias is cast to fp16 as bitween/modules.py:210-211 does."""
+        device = float_layer.weight.device
         q_layer = cls(float_layer.in_features, float_layer.out_features, bits, group_size,
                       bias=float_layer.bias is not None, dtype=torch.float16)
         q_layer = q_layer.to(device)
@@ -94,6 +91,15 @@ class QuantizedLinear(nn.Module):
         if float_layer.bias is not None:
             q_layer.bias.data.copy_(float_layer.bias.data)
         return q_layer
+
+    @classmethod
+    def from_float(cls, float_layer: nn.Linear, bits=8, group_size=32):
+        """RTN-quantize an nn.Linear.  Results are bit-identical to the reference's
+        `deepcopy(layer).to(float32)` -> `quantize_rtn` -> `.copy_()` casts (modules.py:189-213),
+        but the weight is read once in its own dtype by one kernel that writes the packed codes
+        and the fp16 scale / zero_point directly: no fp32 copy of the layer, no temporaries."""
+        buffers = quantize_rtn_to_module_buffers(float_layer.weight.data, bits, group_size)
+        return cls.from_buffers(float_layer, bits, group_size, *buffers)
 
     def __repr__(self):
         return (f"QuantizedLinear(in_features={self.in_features}, out_features={self.out_features}, "

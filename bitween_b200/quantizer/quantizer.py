@@ -5,12 +5,10 @@ Only the RTN branch is part of this library.  Trainable quantization, calibratio
 perplexity / KL evaluation of the reference are outside its scope: asking for them raises or
 prints a notice instead of silently doing something else.
 """
-import copy
-
 import torch
 import torch.nn as nn
 
-from ..modules import QuantizedLinear
+from ..gradual.base_wrapper import copy_without_linears, quantized_linears, replace_leftover_placeholders
 from .func import _set_module
 
 
@@ -37,8 +35,8 @@ class Bitween:
     def quantize(self, evaluate_perplexity=False, eval_samples=100, rtn=False, trainable=False,
                  calib_dataset="pile-10k", nsamples=None, cache_to_disk=None, max_memory_mb=None,
                  ignore_layers=None, batch_size=None, layer_filter=None, **eval_kwargs):
-        """Returns a deep copy of the model with every non-ignored nn.Linear replaced by a
-        QuantizedLinear (quantizer.py:67-84).  As in the reference the branch is keyed on
+        """Returns a copy of the model with every non-ignored nn.Linear replaced by a
+        QuantizedLinear (quantizer.py:67-84); the input model is left untouched.  As in the reference the branch is keyed on
         `trainable`; `rtn` is accepted for signature compatibility.
 
         `layer_filter` (extension): optional callable `(index, name) -> bool`; layers it rejects
@@ -55,21 +53,31 @@ class Bitween:
         if batch_size is not None:
             self.batch_size = batch_size
         try:
-            quantized_model = copy.deepcopy(self.model)
-            index = 0
-            for name, module in list(quantized_model.named_modules()):
-                if not isinstance(module, nn.Linear):
-                    continue
+            # Which layers are quantized is decided first, in module order and with the reference's
+            # printed lines (quantizer.py:72-80); their weights are then NOT deep-copied with the
+            # rest of the model (the reference copies the whole model, quantizer.py:69, and every
+            # layer once more, modules.py:191) and all of them are quantized by one batched launch
+            # per (device, dtype) instead of one launch per layer.
+            state = {"index": 0}
+
+            def keep_as_linear(name, layer):
                 if name in self.ignore_layers:
                     print(f"  - Skipping ignored layer: {name}")
-                    continue
-                take = layer_filter is None or layer_filter(index, name)
-                index += 1
-                if not take:
-                    continue
-                print(f"  - Quantizing layer: {name}")
-                q_module = QuantizedLinear.from_float(module, self.bits, self.group_size)
-                _set_module(quantized_model, name, q_module)
+                    return True
+                take = layer_filter is None or layer_filter(state["index"], name)
+                state["index"] += 1
+                if take:
+                    print(f"  - Quantizing layer: {name}")
+                return not take
+
+            quantized_model, taken = copy_without_linears(self.model, skip=keep_as_linear)
+            q_layers = quantized_linears([layer for _, layer in taken], self.bits, self.group_size)
+            if taken and taken[0][0] == "":
+                quantized_model = q_layers[0]        # the model is a single nn.Linear
+            else:
+                for (name, _), q_module in zip(taken, q_layers):
+                    _set_module(quantized_model, name, q_module)
+                replace_leftover_placeholders(quantized_model)
             print("--- Quantization complete ---")
             if evaluate_perplexity:
                 print("bitween_b200: perplexity / KL evaluation is not part of this library; skipped")

@@ -83,6 +83,32 @@ BW_API int bw_rtn_quantize_pack(const void *w, int w_dtype, int64_t N, int64_t K
                          void *zero_point, int zp_dtype, unsigned flags, void *stream);
 
 /*
+ * RTN quantize + pack of several weight matrices in one call: the per-layer loops of the
+ * reference (bitween/quantizer/quantizer.py:72-80 over a model, bitween/gradual/base_wrapper.py:
+ * 300-311 over a decoder block) call quantize_rtn once per layer; for the handful of linears of
+ * a block the launches, not the kernel, are the cost.  All matrices share the weight dtype, bit
+ * width, group size and output dtypes; shapes differ.  One kernel is launched when every matrix
+ * takes the vector path (group_size a power-of-two multiple of the elements in 16 bytes, up to
+ * 32 such chunks; weights 16-byte and packed words 8-byte aligned), else one per matrix.
+ *   jobs       HOST array of njobs entries (pageable is fine; read before the call returns)
+ *   table_dev  device scratch of bw_rtn_batch_table_bytes(njobs) bytes for the job table, which
+ *              the call copies there with one asynchronous copy on `stream`; must stay untouched
+ *              until the kernel has run.  Not for use inside a stream capture.
+ * Results per matrix are those of bw_rtn_quantize_pack.
+ */
+typedef struct {
+    const void *w;       /* [N,K] weights                      */
+    int32_t *qweight;    /* [N,K*bits/32] out                  */
+    void *scale;         /* [N,K/group_size] out               */
+    void *zero_point;    /* [N,K/group_size] out               */
+    int64_t N, K;
+} bw_rtn_job;
+BW_API size_t bw_rtn_batch_table_bytes(int njobs);
+BW_API int bw_rtn_quantize_pack_batch(const bw_rtn_job *jobs, int njobs, int w_dtype, int bits, int group_size,
+                               int scale_dtype, int zp_dtype, unsigned flags, void *table_dev,
+                               size_t table_bytes, void *stream);
+
+/*
  * Dequantize packed weights: out[n][k] = out_dtype( float(scale) * (float(code) - float(zp)) ).
  * With BW_F32 scale / BW_I32 zero_point / BW_F32 out it replaces bitween/functional.py:47-71
  * (dequantize_rtn); with BW_F16 scale and zero_point and BW_F16 out it replaces the Triton
@@ -122,12 +148,22 @@ BW_API int bw_dequantize(const int32_t *qweight, const void *scale, int scale_dt
  * the persistent TMA-fed decode kernel (one launch; needs K/group_size to be a multiple of 8
  * and 16-byte aligned rows, else the cluster split-K streaming kernel runs), more on the
  * tcgen05 tensor-core GEMM; unusual group sizes run on a slower general kernel, never on the
- * CPU.  bw_qmatmul_workspace_bytes: the prepared activations of the cluster kernel (K rounded
+ * CPU.  The kernels are launched with programmatic dependent launch and fetch packed weights,
+ * scales and zero points BEFORE waiting for the preceding kernel of the stream (only the
+ * activations are read after it): qweight, scale and zero_point must not be written by the one
+ * or two kernels that precede the call on its stream -- put an event or any non-library kernel
+ * between a weight update and the call.
+ * bw_qmatmul_workspace_bytes: the prepared activations of the cluster kernel (K rounded
  * up to a k-chunk x 8*ceil(min(M,64)/8) x 2 bytes), the fp16 cast of the activations for the
  * GEMM (M*K*2), or the decode kernel's row-block shares (320 x 8*ceil(M/8) x 128 x 4 bytes),
  * whichever the call may need most.
  */
 BW_API size_t bw_qmatmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int bits, int group_size);
+/* Same query for given activations: fp16 activations that start on a 16-byte boundary need no
+ * cast for the tensor-core GEMM (x_align = the largest power of two, up to 16, dividing the
+ * address of x), so large prefill calls need no workspace at all. */
+BW_API size_t bw_qmatmul_workspace_bytes_for(int64_t M, int64_t N, int64_t K, int bits, int group_size,
+                                      int x_dtype, int x_align);
 
 BW_API int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K,
                const int32_t *qweight, const void *scale, const void *zero_point,
@@ -146,9 +182,15 @@ BW_API int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t 
  * cudaFree and uses no allocating library routine; the caller still owns x, the packed
  * weights and out.
  *
- * Limit: K (rounded up to a k-chunk of 16*32/bits) * 8*ceil(min(M,64)/8) * 2 bytes must not
- * exceed bw_qmatmul_noalloc_max_scratch_bytes() (2 MiB: e.g. K <= 65536 for M <= 16,
- * K <= 16384 for M >= 57); otherwise BW_ERR_TOO_LARGE is returned and nothing is launched.
+ * Limit: what the kernel that runs needs from the array must not exceed
+ * bw_qmatmul_noalloc_max_scratch_bytes() (2 MiB); otherwise BW_ERR_TOO_LARGE is returned and
+ * nothing is launched.  Nothing is needed by the tensor-core GEMM (more than 32 tokens) on fp16
+ * activations that start on a 16-byte boundary, nor by the general kernel (group sizes that
+ * are not a power of two).  bf16 / fp32 (or misaligned) activations of the GEMM are cast to
+ * fp16 into the array (M*K*2 bytes) when that fits; when it does not, and for up to 32 tokens,
+ * the streaming kernel runs on blocks of at most 64 tokens and needs K (rounded up to a
+ * k-chunk of 16*32/bits) * 8*ceil(min(M,64)/8) * 2 bytes: K <= 65536 for M <= 16, K <= 16384
+ * for M >= 57.
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
  * that device current) -- make that first call before starting a stream capture.
  * All calls on a device share the array and it keeps the last call's contents; every call

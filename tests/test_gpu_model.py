@@ -44,13 +44,25 @@ def test_mixed_precision_opt_style_model_logits():
     rng = np.random.RandomState(7)
     qmodel = model
     captured = {}
-    for n in names:
+    # The gradual flow assigns a configuration to the attention and to the MLP linears of every
+    # block (precision_optimizer.py separates them) and quantizes them through the per-block RTN
+    # loop: here `quantize_block` / `quantized_linears`, one batched launch per group of layers.
+    from bitween_b200.gradual import RTNCache, quantize_block
+    from bitween_b200.gradual.base_wrapper import quantized_linears
+    cache = RTNCache()
+    for block in qmodel.model.decoder.layers:
         bits, g = int(rng.choice([8, 4, 2])), int(rng.choice([32, 64, 128]))
-        # one layer at a time with its own (bits, group): Bitween's loop restricted by layer_filter
-        lin = dict(qmodel.named_modules())[n]
-        ql = QuantizedLinear.from_float(lin, bits=bits, group_size=g)
-        parent = qmodel.get_submodule(n.rsplit(".", 1)[0])
-        setattr(parent, n.rsplit(".", 1)[1], ql)
+        float_q = block.self_attn.q_proj
+        block.self_attn = quantize_block(block.self_attn, bits, g, cache)
+        # the batched call gives the bits of the one-layer-at-a-time call
+        single = QuantizedLinear.from_float(float_q, bits=bits, group_size=g)
+        assert torch.equal(single.qweight, block.self_attn.q_proj.qweight)
+        assert torch.equal(single.scale, block.self_attn.q_proj.scale)
+        assert torch.equal(single.zero_point, block.self_attn.q_proj.zero_point)
+        assert torch.equal(single.bias, block.self_attn.q_proj.bias)
+        bits, g = int(rng.choice([8, 4, 2])), int(rng.choice([32, 64, 128]))
+        block.fc1, block.fc2 = quantized_linears([block.fc1, block.fc2], bits, g, cache)
+    assert len(cache) == 72 and cache.hits == 0
     qlayers = {n: m for n, m in qmodel.named_modules() if isinstance(m, QuantizedLinear)}
     assert len(qlayers) == 72 and {m.bits for m in qlayers.values()} == {2, 4, 8}
 

@@ -499,3 +499,24 @@ def test_autograd_through_quantized_linear():
     ref = (2 * y.detach().float()).half().float() @ w
     assert x.grad is not None and x.grad.dtype == torch.float16
     assert_close_rms(as_f32(x.grad), as_f32(ref), 1e-2)
+
+
+def test_rtn_batched_call_equals_single_calls_bit_for_bit():
+    # bw_rtn_quantize_pack_batch: the linears of a block in one launch (shapes differ, one dtype /
+    # bits / group); a batch that cannot take the vector path falls back to one launch per matrix
+    from bitween_b200.functional import quantize_rtn_many_to_module_buffers
+    gen = torch.Generator(device=DEV).manual_seed(21)
+    shapes = [(768, 768), (3072, 768), (768, 3072), (130, 256), (1, 128)]
+    for dt in (torch.float32, torch.bfloat16, torch.float16):
+        ws = [(torch.randn(n, k, device=DEV, generator=gen) * 0.02).to(dt) for n, k in shapes]
+        ws[1][5, 128:256] = 0.125            # a constant group
+        for bits, g in ((4, 128), (2, 64), (8, 32), (4, 24 if dt == torch.float32 else 128)):
+            if any(k % g for _, k in shapes):
+                ws_use = [w for w in ws if w.shape[1] % g == 0]
+            else:
+                ws_use = ws
+            many = quantize_rtn_many_to_module_buffers(ws_use, bits, g)
+            for w, (q, s, z) in zip(ws_use, many):
+                q1, s1, z1 = quantize_rtn_to_module_buffers(w, bits, g)
+                assert torch.equal(q, q1) and torch.equal(s, s1) and torch.equal(z, z1), (dt, bits, g, tuple(w.shape))
+    assert _lib.lib().bw_device_status() == 0

@@ -68,17 +68,14 @@ def test_pickle_round_trip_and_bitween_alias():
     assert bitween is me and bitween.modules.QuantizedLinear is QuantizedLinear and q2 is quantize_rtn
 
 
-def _oracle_from_float(layer, bits, group_size):
-    """from_float with the oracle doing the arithmetic (test double for the CUDA call)."""
-    w = layer.weight.data.float()
-    q, s, z = oracle.quantize_rtn(to_np(w), oracle.F32, bits, group_size)
-    ql = QuantizedLinear(layer.in_features, layer.out_features, bits, group_size, bias=layer.bias is not None)
-    ql.qweight.copy_(torch.from_numpy(q))
-    ql.scale.copy_(torch.from_numpy(s))
-    ql.zero_point.copy_(torch.from_numpy(z))
-    if layer.bias is not None:
-        ql.bias.data.copy_(layer.bias.data)
-    return ql
+def _oracle_many(weights, bits, group_size):
+    """quantize_rtn_many_to_module_buffers with the oracle doing the arithmetic (test double for
+    the batched CUDA call): fp32 arithmetic, fp16 scale / zero-point buffers."""
+    out = []
+    for w in weights:
+        q, s, z = oracle.quantize_rtn(to_np(w.float()), oracle.F32, bits, group_size)
+        out.append((torch.from_numpy(q), torch.from_numpy(s).half(), torch.from_numpy(z).half()))
+    return out
 
 
 class _Block(nn.Module):
@@ -97,8 +94,8 @@ class _Tiny(nn.Module):
 
 
 def test_bitween_rtn_loop_replaces_linears(monkeypatch):
-    monkeypatch.setattr(QuantizedLinear, "from_float", classmethod(
-        lambda cls, layer, bits=8, group_size=32: _oracle_from_float(layer, bits, group_size)))
+    from bitween_b200.gradual import base_wrapper
+    monkeypatch.setattr(base_wrapper, "quantize_rtn_many_to_module_buffers", _oracle_many)
     model = _Tiny()
     buf = io.StringIO()
     with redirect_stdout(buf):
@@ -117,6 +114,9 @@ def test_bitween_rtn_loop_replaces_linears(monkeypatch):
             rtn=True, ignore_layers=["lm_head"], layer_filter=lambda i, name: i % 2 == 0)
     kinds = [type(m).__name__ for m in (half.layers[0].fc1, half.layers[0].fc2, half.layers[1].fc1, half.layers[1].fc2)]
     assert kinds == ["QuantizedLinear", "Linear", "QuantizedLinear", "Linear"]
+    # the weights that get quantized are not copied on the way; everything else is
+    assert qm.embed_tokens.weight.data_ptr() != model.embed_tokens.weight.data_ptr()
+    assert qm.lm_head.weight.data_ptr() != model.lm_head.weight.data_ptr()
     with pytest.raises(NotImplementedError):
         Bitween(model).quantize(trainable=True)
     with pytest.raises(AssertionError):
@@ -132,3 +132,49 @@ def test_qmatmul_wrapper_validates_before_crossing_abi():
         quantized_matmul_cuda(x, torch.zeros(8, 8, dtype=torch.int32), torch.zeros(8, 2), torch.zeros(8, 2),
                               None, 4, 32)
     assert functional.quantize_rtn is quantize_rtn and modules.QuantizedLinear is QuantizedLinear
+
+
+def test_rtn_wrapper_quantizes_a_block_once_per_config_and_restores_it(monkeypatch):
+    """The per-block RTN loop of the gradual flow (reference bitween/gradual/base_wrapper.py:
+    242-370): first forward quantizes a copy of the block, disable() restores the original, and
+    a repeated (bits, group_size) trial on unchanged weights is served from the cache."""
+    from bitween_b200.gradual import RTNCache, RTNWrapper, base_wrapper, quantize_block
+    calls = []
+
+    def counting(weights, bits, group_size):
+        calls.append(len(weights))
+        return _oracle_many(weights, bits, group_size)
+
+    monkeypatch.setattr(base_wrapper, "quantize_rtn_many_to_module_buffers", counting)
+
+    class _Fwd(_Block):
+        def forward(self, x):
+            return x                                     # the wrapped block's own forward is not under test
+
+    block = _Fwd()
+    cache = RTNCache()
+    wrap = RTNWrapper(block, bits=4, group_size=32, block_name="layers.0", cache=cache)
+    assert (wrap.bits, wrap.group_size, wrap.quantization_applied, wrap.quantized_block) == (4, 32, False, None)
+    x = torch.zeros(1, 64)
+    wrap(x)
+    assert wrap.quantization_applied and calls == [2], "both linears of the block in ONE batched call"
+    assert isinstance(wrap.wrapped_block.fc1, QuantizedLinear) and isinstance(block.fc1, nn.Linear)
+    assert wrap.get_wrapped_block() is block
+    assert repr(wrap) == "RTNWrapper(layers.0, storage=cpu, enabled=True)"
+    wrap.disable()
+    assert wrap.wrapped_block is block and not wrap.quantization_applied and not wrap.enabled
+    # the same trial again: no kernel work, same buffers
+    first = quantize_block(block, 4, 32, cache)
+    again = quantize_block(block, 4, 32, cache)
+    assert calls == [2] and cache.hits >= 4
+    assert again.fc1.qweight.data_ptr() == first.fc1.qweight.data_ptr()
+    # another group size, or a modified weight, is a new entry
+    quantize_block(block, 4, 64, cache)
+    with torch.no_grad():
+        block.fc1.weight.add_(1.0)
+    quantize_block(block, 4, 32, cache)
+    assert calls == [2, 2, 1]
+    # a tiny cache evicts the oldest entries instead of growing
+    small = RTNCache(max_bytes=1)
+    quantize_block(block, 8, 32, small)
+    assert len(small) == 1

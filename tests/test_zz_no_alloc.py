@@ -60,9 +60,11 @@ def test_noalloc_matches_regular_entry_point_on_two_calls_in_a_row():
 
 def test_noalloc_refuses_requests_beyond_its_scratch():
     L = _lib.lib()
-    N, K, M = 8, 32768, 64                      # 32768 * 64 * 2 B = 4 MiB > 2 MiB
+    # 64 bf16 tokens x 32768: neither the GEMM's fp16 cast (4 MiB) nor the streaming kernel's
+    # prepared activations (32768 * 64 * 2 B = 4 MiB) fit the 2 MiB array
+    N, K, M = 8, 32768, 64
     q, s, z = _layer(7, N, K, 4, 128)
-    x = torch.zeros(M, K, dtype=torch.float16, device=DEV)
+    x = torch.zeros(M, K, dtype=torch.bfloat16, device=DEV)
     out = torch.full((M, N), 7.0, dtype=torch.float16, device=DEV)
     with pytest.raises(_lib.BitweenKernelError) as e:
         quantized_matmul_noalloc(x, q, s, z, None, 4, 128, out)
@@ -72,7 +74,25 @@ def test_noalloc_refuses_requests_beyond_its_scratch():
     # the same shape with few tokens fits
     x1 = torch.zeros(8, K, dtype=torch.float16, device=DEV)
     quantized_matmul_noalloc(x1, q, s, z, None, 4, 128, torch.empty(8, N, dtype=torch.float16, device=DEV))
+    # fp16 activations on a 16-byte boundary need no scratch at all for more than 32 tokens
+    quantized_matmul_noalloc(x.half(), q, s, z, None, 4, 128, torch.empty(M, N, dtype=torch.float16, device=DEV))
     # argument errors are reported like the regular entry point's
     assert L.bw_qmatmul_noalloc(None, 1, 4, 8, 64, None, None, None, None, None, 1, 3, 32, None) == 1
     with pytest.raises(ValueError):
         quantized_matmul_noalloc(x1[:, ::2], q, s, z, None, 4, 128, out)
+
+
+@pytest.mark.parametrize("xdt", [torch.float16, torch.bfloat16])
+def test_noalloc_many_tokens_long_rows(xdt):
+    # 256 tokens x 8192: fp16 activations are read in place by the tensor-core GEMM (no scratch);
+    # bf16 activations would need a 4 MiB cast, so blocks of 64 tokens stream through the 1 MiB
+    # of prepared activations instead -- both must agree with the regular entry point
+    q, s, z = _layer(11, 192, 8192, 4, 128)
+    x = torch.from_numpy(synth.normal(12, (256, 8192), 1.0)).to(xdt).to(DEV)
+    ref = quantized_matmul_cuda(x, q, s, z, None, 4, 128)
+    out = torch.empty(256, 192, dtype=torch.float16, device=DEV)
+    for _ in range(2):
+        got = quantized_matmul_noalloc(x, q, s, z, None, 4, 128, out)
+        torch.cuda.synchronize()
+        assert_close_rms(as_f32(got), as_f32(ref), 1e-2, str(xdt))
+    assert _lib.last_qmatmul_kernel() == ("qmm_tc_kernel" if xdt == torch.float16 else "qmm_smallm_kernel")
