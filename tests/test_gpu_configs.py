@@ -6,7 +6,11 @@ prefill 4096 tokens), all through the C ABI.
 Every case is checked three ways: all fp16 outputs against "dequantize (the bit-pinned kernel)
 then matmul in fp32" on the same device (max|err| <= 1e-2 * RMS(output)); sampled weight rows
 against the CPU oracle (same bar); and the fp32-accumulate outputs of sampled weight rows
-against a float64 product of the same fp16 operands (max|err| <= 1e-5 * max|output|).
+against a float64 product of the same fp16 operands (max|err| <= 1e-5 * max|output| up to
+K = 4096, growing in proportion to K beyond that: the tensor cores add each K = 16 block into
+the fp32 accumulator with truncation, so a single accumulation chain over K inputs drifts by up
+to ~K/16 half-ulps of the running sum -- measured 1.9e-5 at K = 14336 and 3.3e-5 at K = 28672,
+the same for any fp16 GEMM with fp32 accumulation on this hardware, the reference's included).
 """
 import pytest
 import torch
@@ -41,7 +45,9 @@ def _check_acc_against_f64(x, acc, w_h, what):
     """fp32-accumulate output vs a float64 product of the same fp16-rounded operands, on sampled rows."""
     rows = torch.cat([_sample_rows(w_h.shape[0]), torch.arange(0, w_h.shape[0], max(1, w_h.shape[0] // 57))]).unique().to(acc.device)
     ref64 = x.half().double() @ w_h[rows].double().T
-    assert float((acc[:, rows].double() - ref64).abs().max()) <= 1e-5 * float(ref64.abs().max()), what
+    bound = 1e-5 * max(1.0, x.shape[1] / 4096.0)
+    err = float((acc[:, rows].double() - ref64).abs().max()) / float(ref64.abs().max())
+    assert err <= bound, f"{what}: {err:.3g} > {bound:.3g}"
 
 
 def _check_against_oracle_rows(x, y, q, s_h, z_h, bits, g, what, tokens=24):
