@@ -1,31 +1,32 @@
 #!/usr/bin/env python3
 """Benchmark of the quantized hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode8b|tp70b]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Headline metric: W4 g128 decode qmatmul throughput in GB/s of ALGORITHMIC bytes
-(packed weights + fp16 scale/zero-point + activations in + outputs out, per launch).
+Headline (the `value` of the JSON line): W4 g128 decode qmatmul throughput in GB/s of ALGORITHMIC
+bytes (packed weights + fp16 scale/zero-point + activations in + outputs out, per launch).  One
+step = one decode pass of M in {1,2,4,8,16} tokens over a stack of Llama-3-8B-shaped W4 g128
+linears (4096->4096, 4096->1024, 4096->14336, 14336->4096), `--layers` distinct copies of each so
+that every launch reads weights that are not in L2.  With N > 1 GPUs every rank runs that step on
+its own layer copies -- REPLICAS, no collective on the data path; the line says so.
 
-Workloads
-  decode8b   (default) one step = one decode pass of M in {1,2,4,8,16} tokens over a stack of
-             Llama-3-8B-shaped W4 g128 linears (4096->4096, 4096->1024, 4096->14336,
-             14336->4096), `--layers` distinct copies of each so that every launch reads weights
-             that are not in L2 (the stack is several times the 126 MB L2).  With N GPUs every
-             rank runs the step on its own layers (layers are independent: no collective on the
-             data path, weak scaling; value = bytes of all ranks / max-over-ranks time).
-  tp70b      one step = decode batch 64 through the seven W4 g128 linears of Llama-3-70B-shaped
-             decoder layers, tensor-parallel over N GPUs (column-parallel q/k/v/gate/up,
-             row-parallel o/down + NCCL all-reduce), strong scaling.  At N > 1 the default run
-             also executes it and reports it under extra.tp70b.
+What scales over GPUs is reported under `extra.tp70b` at EVERY N, N = 1 included, on a fixed
+problem (strong scaling): Llama-3-70B-shaped decoder layers (hidden 8192, 64 q / 8 kv heads x 128,
+FFN 28672), W4 g128, tensor-parallel over the N ranks (column-parallel q/k/v/gate/up, row-parallel
+o/down, one NCCL all-reduce after each row-parallel linear), decode batch 64 and prefill 4096
+tokens, with the time per decoder layer and the all-reduces' share of it; plus RTN quantize+pack
+over the weights of 80 such layers, sharded by layer with no communication.
+
 Synthetic data: weights ~ N(0, 0.02) rounded to bf16 and RTN-quantized on the device by this
 library's own kernel; activations ~ N(0, 1) bf16.  No checkpoint or dataset is involved.
 
-The line printed by rank 0 carries `value` (inputs resident in HBM), `e2e` (the same work
-through the host-buffer call: pinned host activations in, host outputs back, copies inside the
-timed region), `roofline` for the decode kernel against the measured HBM peak, and
-`cpu_baseline` (the CPU oracle on the host cores over a bounded sample).  `--impl reference`
-times the CPU implementation of the same path instead (the oracle port of the reference's
-CPU code; the reference's own forward cannot run without a GPU).
+The line carries `value` (inputs resident in HBM), `e2e` (the same work through the host-buffer
+call: pinned host activations in, host outputs back, copies inside the timed region), `roofline`
+for the decode kernel against the measured HBM peak, `cpu_baseline` (the CPU oracle on the host
+cores over a bounded sample) and, under `extra`, RTN GB/s, W8 decode, the prefill grid
+(M in {512, 2048, 8192} x {W4 g128, W2 g64} x the four shapes) and decode at 64 tokens.
+`--impl reference` times the CPU implementation of the same path instead (the oracle port of the
+reference's CPU code; the reference's own forward cannot run without a GPU).
 """
 import argparse
 import json
@@ -43,6 +44,18 @@ LLAMA8B_SHAPES = [("q_o_proj", 4096, 4096), ("kv_proj", 1024, 4096), ("gate_up_p
                   ("down_proj", 4096, 14336)]
 DECODE_M = [1, 2, 4, 8, 16]
 FALLBACK_HBM_GBS = 6650.0
+
+# Llama-3-70B decoder linears: (name, out_features, in_features, tensor-parallel mode)
+HIDDEN70, KV70, FFN70 = 8192, 1024, 28672
+LLAMA70B_LINEARS = [("q_proj", HIDDEN70, HIDDEN70, "column"), ("k_proj", KV70, HIDDEN70, "column"),
+                    ("v_proj", KV70, HIDDEN70, "column"), ("o_proj", HIDDEN70, HIDDEN70, "row"),
+                    ("gate_proj", FFN70, HIDDEN70, "column"), ("up_proj", FFN70, HIDDEN70, "column"),
+                    ("down_proj", HIDDEN70, FFN70, "row")]
+
+# DRAM bytes of one qmm_decode_kernel launch divided by its algorithmic bytes, from ncu captures
+# of single launches (dram__bytes_read.sum + dram__bytes_write.sum) at 1 and 16 tokens; constants
+# from those profiles, not measured during the run.
+DECODE_TRAFFIC_FACTOR = {"q_o_proj": 1.004, "kv_proj": 1.02, "gate_up_proj": 1.001, "down_proj": 1.001}
 
 
 def decode_bytes(M, N, K, bits, g, bias=False):
@@ -127,6 +140,15 @@ class ClockSampler:
 # CPU arm: the oracle port of the reference's CPU code, all host threads
 # ------------------------------------------------------------------------------------------
 
+def cpu_threads():
+    """All host threads for the CPU oracle, whatever the launcher exported (torchrun forces
+    OMP_NUM_THREADS=1 on its workers)."""
+    from oracle import oracle
+    n = os.cpu_count() or 1
+    oracle.set_num_threads(n)
+    return oracle.num_threads()
+
+
 def cpu_decode_sample(sample_shapes, Ms, bits=4, g=128, repeats=1):
     """Times the CPU oracle (quantized forward = dequantize + matmul, restating the reference's
     bitween/functional.py:47-71 + bitween/modules.py:97-101) on a bounded sample."""
@@ -154,6 +176,7 @@ def run_reference_arm(args, rank):
         return
     from oracle import oracle
     oracle.build()
+    cores = cpu_threads()
     sample = [LLAMA8B_SHAPES[1], LLAMA8B_SHAPES[0]]      # 4096->1024 and 4096->4096
     Ms = DECODE_M
     for _ in range(args.warmup):
@@ -164,7 +187,6 @@ def run_reference_arm(args, rank):
         t_all += s
         b_all += b
     val = b_all / t_all / 1e9
-    cores = oracle.num_threads()
     desc = "M in {1,2,4,8,16} x {4096->1024, 4096->4096} W4 g128 per step (bounded sample of the decode sweep)"
     line = {"impl": "reference", "metric": "w4g128_qmatmul_decode_GBps", "value": val, "unit": "GB/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -201,6 +223,30 @@ def time_region(torch, fn, stream=None):
     return e0.elapsed_time(e1)
 
 
+def max_over_ranks(torch, dist, device, ms):
+    if dist is None:
+        return ms
+    t = torch.tensor([ms], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def graph_ms(torch, body, flush=None, reps=5):
+    """CUDA-event time (ms) of one replay of `body` captured as a CUDA graph, L2 flushed before each replay."""
+    body()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        body()
+    g.replay()
+    total = 0.0
+    for _ in range(reps):
+        if flush is not None:
+            flush.fill_(1)
+        total += time_region(torch, g.replay)
+    return total / reps
+
+
 def run_decode8b(args, torch, dist, rank, world, device):
     from bitween_b200 import functional as fn
     from bitween_b200.kernels import _lib
@@ -222,11 +268,12 @@ def run_decode8b(args, torch, dist, rank, world, device):
 
     calls_per_step = len(DECODE_M) * args.layers * len(LLAMA8B_SHAPES)
     launches_per_step = calls_per_step                      # the decode kernel is the only launch of a call
-    bytes_per_step = sum(decode_bytes(M, N, K, bits, g) for M in DECODE_M for (_, N, K) in LLAMA8B_SHAPES) * args.layers
+    per_shape = {name: sum(decode_bytes(M, N, K, bits, g) for M in DECODE_M) for (name, N, K) in LLAMA8B_SHAPES}
+    bytes_per_step = sum(per_shape.values()) * args.layers
+    traffic_per_step = sum(per_shape[n] * DECODE_TRAFFIC_FACTOR[n] for n in per_shape) * args.layers
 
     for _ in range(max(args.warmup, 1) if not args.graph else 1):
         step()
-    graph = None
     if args.graph:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
@@ -244,10 +291,7 @@ def run_decode8b(args, torch, dist, rank, world, device):
     sampler.start()
     ms = time_region(torch, lambda: [run_step() for _ in range(args.steps)])
     clocks = sampler.stop()
-    if dist is not None:
-        t = torch.tensor([ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms = max_over_ranks(torch, dist, device, ms)
     value = bytes_per_step * args.steps * world / (ms * 1e-3) / 1e9
     decode_kernel = _lib.last_qmatmul_kernel()
 
@@ -266,11 +310,7 @@ def run_decode8b(args, torch, dist, rank, world, device):
     for _ in range(2):
         e2e_step()
     e2e_steps = max(1, min(args.steps, 5))
-    ms_e2e = time_region(torch, lambda: [e2e_step() for _ in range(e2e_steps)])
-    if dist is not None:
-        t = torch.tensor([ms_e2e], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_e2e = float(t.item())
+    ms_e2e = max_over_ranks(torch, dist, device, time_region(torch, lambda: [e2e_step() for _ in range(e2e_steps)]))
     e2e_val = bytes_per_step * e2e_steps * world / (ms_e2e * 1e-3) / 1e9
 
     # ---- per-shape breakdown (M = 1 and 16): the layer copies of one shape replayed as one graph,
@@ -284,67 +324,37 @@ def run_decode8b(args, torch, dist, rank, world, device):
                     for stack in layers:
                         L = stack[si]
                         quantized_matmul_cuda(xs[M][K], L.q, L.scale, L.zp, None, bits, g, out=outs[M][N])
-                one()
-                torch.cuda.synchronize()
-                run_one = one
-                if args.graph:
-                    g1 = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g1):
-                        one()
-                    run_one = g1.replay
-                for _ in range(3):
-                    run_one()
-                reps, t_ms = 10, 0.0
-                for _ in range(reps):
-                    flush.fill_(1)                      # 256 MB written: evicts the layer copies from L2
-                    t_ms += time_region(torch, run_one)
-                t_ms /= reps * args.layers
+                t_ms = graph_ms(torch, one, flush, reps=10) / args.layers
                 breakdown[f"{name}_{N}x{K}_M{M}"] = {
                     "us": round(t_ms * 1e3, 2),
                     "GBps": round(decode_bytes(M, N, K, bits, g) / (t_ms * 1e-3) / 1e9, 1)}
 
-    extra = {}
-    if rank == 0 and not args.no_extra:
-        extra = run_extras(args, torch, fn, quantized_matmul_cuda, device, gen)
-
+    config = {"workload": "decode8b", "shapes": "Llama-3-8B linears x M{1,2,4,8,16}",
+              "bits": bits, "group_size": g, "layer_copies": args.layers,
+              "l2_policy": f"inputs larger than L2: {args.layers} distinct copies of every layer "
+                           f"({args.layers * 69} MB of packed weights per pass)",
+              "cuda_graph": bool(args.graph)}
+    if world > 1:
+        config["parallelism"] = (f"replicas x{world}: every rank runs the sweep on its own layer copies, no collective "
+                                 "(the tensor-parallel workload is extra.tp70b)")
     return {"value": value, "ms": ms, "launches": launches_per_step * args.steps, "calls": calls_per_step * args.steps,
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps},
             "bytes_per_launch": bytes_per_step / calls_per_step, "launches_per_step": launches_per_step,
-            "breakdown": breakdown, "extra": extra, "kernel": decode_kernel,
-            # DRAM bytes of one launch from the committed ncu capture of the 14336x4096 M=1 launch
-            # (31.27 MB read + 0 written against 31.23 MB algorithmic), scaled to the average launch
-            "traffic": bytes_per_step / calls_per_step * (31.27 / 31.23),
-            "traffic_source": "ncu capture profiles/qmm_decode_kernel_14336x4096_w4g128.md: dram bytes = 1.001 x "
-                              "algorithmic bytes, scaled to the average launch of the sweep",
-            "config": {"workload": "decode8b", "shapes": "Llama-3-8B linears x M{1,2,4,8,16}",
-                       "bits": bits, "group_size": g, "layer_copies": args.layers,
-                       "l2_policy": f"inputs larger than L2: {args.layers} distinct copies of every layer "
-                                    f"({args.layers * 69} MB of packed weights per pass)",
-                       "cuda_graph": bool(args.graph)}}
+            "breakdown": breakdown, "kernel": decode_kernel,
+            "traffic": traffic_per_step / calls_per_step,
+            "traffic_source": "constant from ncu profiles of single launches (DRAM bytes / algorithmic bytes per shape: "
+                              + ", ".join(f"{k} {v}" for k, v in DECODE_TRAFFIC_FACTOR.items()) + "), weighted over the sweep",
+            "config": config}
 
 
-def graph_ms(torch, body, flush=None, reps=5):
-    """CUDA-event time (ms) of one replay of `body` captured as a CUDA graph, L2 flushed before each replay."""
-    body()
-    torch.cuda.synchronize()
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
-        body()
-    g.replay()
-    total = 0.0
-    for _ in range(reps):
-        if flush is not None:
-            flush.fill_(1)
-        total += time_region(torch, g.replay)
-    return total / reps
-
-
-def run_extras(args, torch, fn, qmm, device, gen):
-    """RTN quantize+pack GB/s, W8 g128 decode GB/s and prefill TFLOP/s on the same shapes (reported, not
-    the headline).  Every measurement replays a CUDA graph of launches on distinct layer copies with the
-    L2 flushed (256 MB written) before each replay."""
+def run_single_gpu_extras(args, torch, device, gen):
+    """RTN quantize+pack GB/s, W8 g128 decode GB/s, decode at 64 tokens and the prefill grid on the
+    Llama-3-8B shapes (reported, not the headline).  Every measurement replays a CUDA graph of
+    launches on distinct layer copies with the L2 flushed (256 MB written) before each replay."""
+    from bitween_b200 import functional as fn
+    from bitween_b200.kernels.cuda_loader import quantized_matmul_cuda as qmm
     out = {}
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     # RTN: bf16 weights, fp32 arithmetic, fp32 scale + int32 zero-point out
@@ -361,8 +371,9 @@ def run_extras(args, torch, fn, qmm, device, gen):
         del ws
     out["rtn_w4g128_bf16in_GBps"] = round(tot_b / (tot_ms * 1e-3) / 1e9, 1)
     out["rtn_per_shape_GBps"] = per
-    # W8 g128 decode (the second weight format of the decode configuration), M = 1 and 16
-    w8 = {}
+    # W8 g128 decode (the second weight format of the decode configuration), M = 1 and 16;
+    # W4 g128 at 64 tokens (the tensor-parallel decode batch) on the same shapes
+    w8, d64 = {}, {}
     for (name, N, K) in LLAMA8B_SHAPES:
         layers = [Layer(N, K, 8, 128, device, gen, torch, fn) for _ in range(4)]
         for M in (1, 16):
@@ -371,19 +382,167 @@ def run_extras(args, torch, fn, qmm, device, gen):
             ms = graph_ms(torch, lambda: [qmm(x, L.q, L.scale, L.zp, None, 8, 128, out=y) for L in layers], flush) / len(layers)
             w8[f"{name}_{N}x{K}_M{M}"] = round(decode_bytes(M, N, K, 8, 128) / (ms * 1e-3) / 1e9, 1)
         del layers
+        layers = [Layer(N, K, 4, 128, device, gen, torch, fn) for _ in range(4)]
+        x = torch.randn(64, K, device=device, generator=gen).to(torch.bfloat16)
+        y = torch.empty(64, N, device=device, dtype=torch.float16)
+        ms = graph_ms(torch, lambda: [qmm(x, L.q, L.scale, L.zp, None, 4, 128, out=y) for L in layers], flush) / len(layers)
+        d64[f"{name}_{N}x{K}_M64"] = round(decode_bytes(64, N, K, 4, 128) / (ms * 1e-3) / 1e9, 1)
+        del layers
     out["decode_w8g128_GBps"] = w8
-    # prefill
-    pf = {}
-    for (name, N, K) in LLAMA8B_SHAPES:
-        L = Layer(N, K, 4, 128, device, gen, torch, fn)
-        for M in (args.prefill_m,):
-            x = torch.randn(M, K, device=device, generator=gen).to(torch.float16)
-            y = torch.empty(M, N, device=device, dtype=torch.float16)
-            ms = graph_ms(torch, lambda: [qmm(x, L.q, L.scale, L.zp, None, 4, 128, out=y) for _ in range(3)], flush) / 3
-            pf[f"{name}_{N}x{K}_M{M}"] = round(2.0 * M * N * K / (ms * 1e-3) / 1e12, 1)
-        del L
-    out["prefill_w4g128_TFLOPs"] = pf
+    out["decode_w4g128_M64_GBps"] = d64
+    # prefill grid: bf16 activations (cast to fp16 by the library, as the reference does)
+    for bits, g in ((4, 128), (2, 64)):
+        pf = {}
+        for (name, N, K) in LLAMA8B_SHAPES:
+            L = Layer(N, K, bits, g, device, gen, torch, fn)
+            for M in (512, 2048, 8192):
+                x = torch.randn(M, K, device=device, generator=gen).to(torch.bfloat16)
+                y = torch.empty(M, N, device=device, dtype=torch.float16)
+                ms = graph_ms(torch, lambda: [qmm(x, L.q, L.scale, L.zp, None, bits, g, out=y) for _ in range(3)], flush, reps=3) / 3
+                pf[f"{name}_{N}x{K}_M{M}"] = round(2.0 * M * N * K / (ms * 1e-3) / 1e12, 1)
+                del x, y
+            del L
+        out[f"prefill_w{bits}g{g}_TFLOPs"] = pf
     return out
+
+
+def shard_shape(N, K, mode, world):
+    return (N // world, K) if mode == "column" else (N, K // world)
+
+
+def run_tp70b(args, torch, dist, rank, world, device):
+    """Llama-3-70B-shaped decoder layers, tensor-parallel over the ranks, a FIXED number of layers
+    at every N (strong scaling): decode batch 64 and prefill 4096 tokens; RTN over 80 layers'
+    weights sharded by layer.  Returns the dict reported under extra.tp70b."""
+    from bitween_b200 import functional as fn
+    from bitween_b200 import tp
+    from bitween_b200.kernels import _lib
+    from bitween_b200.kernels.cuda_loader import quantized_matmul_cuda as qmm
+    bits, g = 4, 128
+    layers_n = args.tp_layers
+    gen = torch.Generator(device=device).manual_seed(4321 + rank)
+    layers = []
+    for _ in range(layers_n):
+        lay = []
+        for (name, N, K, mode) in LLAMA70B_LINEARS:
+            n, k = shard_shape(N, K, mode, world)
+            w = (torch.randn(n, k, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+            q, s, z = fn.quantize_rtn_to_module_buffers(w, bits, g)
+            lay.append((name, mode, n, k, q, s, z))
+            del w
+        layers.append(lay)
+    shard_bytes = sum(n * k // 2 for (_, _, n, k, _, _, _) in layers[0])
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    res = {"parallelism": f"tp{world}", "layers": layers_n, "scaling": "strong",
+           "packed_MB_per_rank_per_layer": round(shard_bytes / 1e6, 1)}
+
+    def measure(M, allreduce, use_graph, chunks=1, steps=None):
+        ks = {k for (_, _, _, k, _, _, _) in layers[0]}
+        ns = {n for (_, _, n, _, _, _, _) in layers[0]}
+        xs = {k: torch.randn(M, k, device=device, generator=gen).to(torch.bfloat16) for k in ks}
+        outs = {n: torch.empty(M, n, device=device, dtype=torch.float16) for n in ns}
+        comm = torch.cuda.Stream(device=device) if chunks > 1 else None
+
+        def step():
+            for lay in layers:
+                for (name, mode, n, k, q, s, z) in lay:
+                    if mode == "row" and allreduce and dist is not None and chunks > 1:
+                        # GEMM of token chunk i+1 while the all-reduce of chunk i runs on a second stream
+                        main = torch.cuda.current_stream(device)
+                        bounds = [M * i // chunks for i in range(chunks + 1)]
+                        for i in range(chunks):
+                            lo, hi = bounds[i], bounds[i + 1]
+                            qmm(xs[k][lo:hi], q, s, z, None, bits, g, out=outs[n][lo:hi])
+                            ev = torch.cuda.Event()
+                            ev.record(main)
+                            with torch.cuda.stream(comm):
+                                comm.wait_event(ev)
+                                dist.all_reduce(outs[n][lo:hi])
+                        main.wait_stream(comm)
+                    else:
+                        y = qmm(xs[k], q, s, z, None, bits, g, out=outs[n])
+                        if mode == "row" and allreduce and dist is not None:
+                            dist.all_reduce(y)
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        run_step = step
+        if use_graph:
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    step()
+                run_step = graph.replay
+            except Exception:   # noqa: BLE001  (a collective that cannot be captured: report eager only)
+                torch.cuda.synchronize()
+                return None
+        for _ in range(3):
+            run_step()
+        steps = steps or (10 if M > 1024 else 30)
+        if dist is not None:
+            dist.barrier()
+        total = 0.0
+        for _ in range(steps):
+            flush.fill_(1)
+            total += time_region(torch, run_step)
+        return max_over_ranks(torch, dist, device, total / steps)
+
+    algo = {M: world * layers_n * sum(decode_bytes(M, n, k, bits, g) for (_, _, n, k, _, _, _) in layers[0]) for M in (64, 4096)}
+    flops = {M: 2.0 * M * layers_n * sum(N * K for (_, N, K, _) in LLAMA70B_LINEARS) for M in (64, 4096)}
+    # decode batch 64: eager and CUDA-graph replays, with and without the all-reduces
+    dec = {}
+    for label, graph in (("eager", False), ("graph", True)):
+        ms = measure(64, True, graph)
+        if ms is not None:
+            dec[label] = ms
+    best = min(dec, key=dec.get)
+    ms_no_ar = measure(64, False, best == "graph") if world > 1 else dec[best]
+    res["decode64"] = {
+        "GBps": round(algo[64] / (dec[best] * 1e-3) / 1e9, 1), "us_per_layer": round(dec[best] * 1e3 / layers_n, 1),
+        "us_per_layer_without_allreduce": round(ms_no_ar * 1e3 / layers_n, 1),
+        "allreduce_share": round(max(0.0, 1.0 - ms_no_ar / dec[best]), 3), "mode": best,
+        "us_per_layer_by_mode": {k: round(v * 1e3 / layers_n, 1) for k, v in dec.items()},
+        "kernel": _lib.last_qmatmul_kernel(), "allreduce_bytes": 64 * HIDDEN70 * 2}
+    # prefill 4096 tokens: plain, and with the row-parallel GEMMs chunked against their all-reduces
+    pf = {"plain": measure(4096, True, False)}
+    if world > 1:
+        pf["overlap4"] = measure(4096, True, False, chunks=4)
+        pf_no_ar = measure(4096, False, False)
+    else:
+        pf_no_ar = pf["plain"]
+    bestp = min(pf, key=pf.get)
+    res["prefill4096"] = {
+        "TFLOPs": round(flops[4096] / (pf[bestp] * 1e-3) / 1e12, 1), "ms_per_layer": round(pf[bestp] / layers_n, 3),
+        "ms_per_layer_without_allreduce": round(pf_no_ar / layers_n, 3),
+        "allreduce_share": round(max(0.0, 1.0 - pf_no_ar / pf[bestp]), 3), "mode": bestp,
+        "ms_per_layer_by_mode": {k: round(v / layers_n, 3) for k, v in pf.items()},
+        "allreduce_bytes": 4096 * HIDDEN70 * 2}
+    del layers
+
+    # RTN quantize+pack over the weights of 80 decoder layers, layer l on rank l % world, generated
+    # layer by layer (never more than one layer of bf16 weights resident), no communication
+    total_ms, total_b, mine = 0.0, 0, 0
+    for layer in range(args.rtn_layers):
+        if layer % world != rank:
+            continue
+        g2 = torch.Generator(device=device).manual_seed(9000 + layer)
+        ws = [(torch.randn(N, K, device=device, generator=g2) * 0.02).to(torch.bfloat16) for (_, N, K, _) in LLAMA70B_LINEARS]
+        if mine == 0:
+            fn.quantize_rtn_many_to_module_buffers(ws, bits, g)          # warm-up
+        total_ms += time_region(torch, lambda: fn.quantize_rtn_many_to_module_buffers(ws, bits, g))
+        total_b += sum(N * K * 2 + N * K * bits // 8 + N * (K // g) * 4 for (_, N, K, _) in LLAMA70B_LINEARS)
+        mine += 1
+        del ws
+    total_ms = max_over_ranks(torch, dist, device, total_ms)
+    if dist is not None:
+        t = torch.tensor([float(total_b)], device=device, dtype=torch.float64)
+        dist.all_reduce(t)
+        total_b = float(t.item())
+    res["rtn80"] = {"GBps": round(total_b / (total_ms * 1e-3) / 1e9, 1), "layers": args.rtn_layers,
+                    "ms_slowest_rank": round(total_ms, 2),
+                    "what": "bf16 weights in, packed W4 g128 + fp16 scale + fp16 zero point out, the seven linears of a layer "
+                            "per batched launch through the Python API; allocation of the outputs inside the timed region"}
+    return res
 
 
 def main():
@@ -392,11 +551,10 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="auto")
     ap.add_argument("--layers", type=int, default=8, help="distinct copies of each layer shape (L2 defeat)")
     ap.add_argument("--graph", type=int, default=1, help="replay each step as one CUDA graph")
-    ap.add_argument("--prefill-m", type=int, default=2048)
-    ap.add_argument("--tp-tokens", type=int, default=64, help="decode batch of the tp70b workload")
+    ap.add_argument("--tp-layers", type=int, default=3, help="70B-shaped decoder layers of the tensor-parallel workload")
+    ap.add_argument("--rtn-layers", type=int, default=80, help="70B-shaped layers whose weights the sharded RTN run quantizes")
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -421,44 +579,22 @@ def main():
         dist_mod.init_process_group("nccl", device_id=device)
         dist = dist_mod
 
-    workload = args.workload
-    if workload == "auto":
-        workload = "decode8b"
-    if workload == "decode8b":
-        # The decode sweep shards over GPUs by layer: every rank streams its own layers, no
-        # collective on the data path (weak scaling).  With more than one GPU the tensor-parallel
-        # 70B-shaped workload (strong scaling, NCCL all-reduce after the row-parallel layers) runs
-        # afterwards and is reported under extra.tp70b.
-        res = run_decode8b(args, torch, dist, rank, world, device)
-        scaling = "weak"
-        if world > 1:
-            res["config"]["parallelism"] = f"dp{world}: each rank runs the sweep on its own layer copies, no collective"
-            if not args.no_extra:
-                import copy
-                from bitween_b200 import tp_bench
-                targs = copy.copy(args)
-                targs.steps = min(args.steps, 30)
-                tp = tp_bench.run_tp70b(targs, torch, dist, rank, world, device, ClockSampler, time_region, decode_bytes)
-                res.setdefault("extra", {})["tp70b"] = {
-                    "metric": "w4g128_qmatmul_decode_GBps", "value": tp["value"], "unit": "GB/s", "scaling": "strong",
-                    "ms_per_step": tp["ms"] / targs.steps, "steps": targs.steps, "kernel": tp["kernel"],
-                    "e2e": tp["e2e"], "config": tp["config"]}
-    elif workload == "tp70b":
-        from bitween_b200 import tp_bench
-        res = tp_bench.run_tp70b(args, torch, dist, rank, world, device, ClockSampler, time_region, decode_bytes)
-        scaling = "strong"
-    else:
-        raise SystemExit(f"unknown workload {workload}")
+    res = run_decode8b(args, torch, dist, rank, world, device)
+    extra = {}
+    if not args.no_extra:
+        extra["tp70b"] = run_tp70b(args, torch, dist, rank, world, device)
+        if rank == 0 and world == 1:
+            extra.update(run_single_gpu_extras(args, torch, device, torch.Generator(device=device).manual_seed(77)))
 
     if rank == 0:
         peaks = read_peaks()
-        # the roofline is stated per qmatmul call (one launch of the dominant kernel, plus the
-        # activation cast where a call has one), its duration the call's share of the timed region
+        # the roofline is stated per qmatmul call (one launch of the decode kernel), its duration
+        # the call's share of the timed region
         ms_per_launch = res["ms"] / max(res["calls"], 1)
         achieved = res["bytes_per_launch"] / (ms_per_launch * 1e-3) / 1e9
         line = {"metric": "w4g128_qmatmul_decode_GBps", "value": res["value"], "unit": "GB/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": res["ms"] / args.steps, "higher_is_better": True, "scaling": scaling,
+                "ms_per_step": res["ms"] / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": res["config"],
                 "clocks": res["clocks"], "e2e": res["e2e"], "gpu_launches": res["launches"],
                 "roofline": {"bound": "hbm", "kernel": res["kernel"], "achieved": achieved,
@@ -467,14 +603,15 @@ def main():
                              "traffic_source": res.get("traffic_source"),
                              "us_per_launch": ms_per_launch * 1e3,
                              "algorithmic_bytes_per_launch": res["bytes_per_launch"]},
-                "breakdown": res.get("breakdown", {}), "extra": res.get("extra", {})}
+                "breakdown": res.get("breakdown", {}), "extra": extra}
         if world == 1 and not args.no_cpu:
             from oracle import oracle
             oracle.build()
+            cores = cpu_threads()
             cpu_decode_sample(LLAMA8B_SHAPES[1:2], [1])
             b, s = cpu_decode_sample(LLAMA8B_SHAPES, DECODE_M, repeats=4)
             line["cpu_baseline"] = {
-                "value": b / s / 1e9, "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
+                "value": b / s / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
                 "sample": "the whole decode sweep (M in {1,2,4,8,16} x the four Llama-3-8B shapes, W4 g128), "
                           f"4 repeats, one layer copy ({s:.1f} s of CPU time); oracle port of the reference's "
                           "CPU dequantize + matmul, OpenMP over all host threads"}

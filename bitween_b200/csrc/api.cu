@@ -48,9 +48,6 @@ bool decode_path_ok(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K,
 size_t decode_workspace_bytes(int64_t M, int64_t N, int64_t K, int bits);
 int decode_device_status();
 void set_decode_tuning(int enabled, int smem_kb, int max_ctas, int pdl);
-#ifdef BW_TUNING
-void set_decode_trace(unsigned long long *buf);
-#endif
 int qmatmul_decode(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
                    const __half *scale, const __half *zp, const __half *bias, void *out, int out_dtype,
                    int bits, int g, void *workspace, cudaStream_t st);
@@ -345,7 +342,6 @@ BW_API void bw_debug_set_smallm_tuning(int rt, int warps, int splits) { set_smal
 BW_API void bw_debug_set_pdl(int on) { set_smallm_pdl(on); }
 BW_API void bw_debug_set_decode(int enabled, int smem_kb, int max_ctas, int pdl) { set_decode_tuning(enabled, smem_kb, max_ctas, pdl); }
 BW_API void bw_debug_set_tc(int on) { set_tc_enabled(on); }
-BW_API void bw_debug_set_decode_trace(void *buf) { set_decode_trace((unsigned long long *)buf); }
 BW_API void bw_debug_set_tc_splits(int s) { set_tc_splits(s); }
 BW_API void bw_debug_set_tc_min_tokens(int m) { g_tc_min_tokens = m; }
 #endif

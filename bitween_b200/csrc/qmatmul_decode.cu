@@ -84,16 +84,7 @@ struct DecParams {
     int raw_bytes;        // raw activation bytes per tile
     int cluster;          // CTAs per row block when they form a thread-block cluster (sums through DSMEM), else 1
     int cluster_leader;   // 1: the cluster's first CTA collects the shares; 0: every CTA collects one slice
-#ifdef BW_TUNING
-    unsigned long long *trace;   // tuning builds: per-CTA timestamps, or null
-#endif
 };
-#ifdef BW_TUNING
-unsigned long long *g_dec_trace_host = nullptr;
-#define DK_TRACE(slot) do { if (p.trace) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.trace[(size_t)blockIdx.x * 32 + (slot)] = t_; } } while (0)
-#else
-#define DK_TRACE(slot) do { } while (0)
-#endif
 
 template <int BITS> struct DecGeom {
     static constexpr int VPI = 32 / BITS;
@@ -262,7 +253,6 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     constexpr int NRED = MT == 4 ? 1 : 2;             // hand-over buffers
     extern __shared__ unsigned char smem_dyn[];
     pdl_launch_dependents();
-    if (threadIdx.x == 0) DK_TRACE(0);
 
     const int S = p.stages;
     unsigned char *base = smem_dyn + ((1024u - (smem_addr(smem_dyn) & 1023u)) & 1023u);   // swizzled tiles: 1024-byte aligned
@@ -277,8 +267,8 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     uint64_t *cdone = xdone + DK_MAX_STAGES;                          // [1] the peers' shares of this CTA's slice have arrived
     uint64_t *red_full = cdone + 1;                     // [2] consumers -> hand-over warps
     uint64_t *red_free = red_full + 2;                               // [2] hand-over warps -> consumers
-    volatile int *flags = reinterpret_cast<volatile int *>(red_free + 2);   // [0] a wait ran out, [1] last arriver, [2] c_lo, [3] nc, [4..7] row block left to the whole CTA to sum: flag, rb, c_lo, nc
-    int *slots = const_cast<int *>(flags) + 8;                       // [DK_MAX_CTAS] scratch slots of one row block's shares
+    volatile int *flags = reinterpret_cast<volatile int *>(red_free + 2);   // [0] a wait ran out, [1] last arriver, [2] c_lo, [3] nc
+    int *slots = const_cast<int *>(flags) + 4;                       // [DK_MAX_CTAS] scratch slots of one row block's shares
     float4 *cpart = reinterpret_cast<float4 *>(                      // [cluster ranks][slice] the peers' shares of this CTA's slice of the outputs
         (reinterpret_cast<uintptr_t>(slots + DK_MAX_CTAS) + 15) & ~(uintptr_t)15);
     volatile int *dead = flags;
@@ -299,7 +289,6 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
         for (int b = 0; b < 2; ++b) { mbar_init(red_full + b, DK_CWARPS); mbar_init(red_free + b, 1); }
         mbar_init(cdone, (unsigned)(p.cluster > 1 ? (p.cluster - 1) * DK_HWARPS : 1));   // one arrival per peer hand-over warp
         flags[0] = 0;
-        flags[4] = 0;
     }
     if (threadIdx.x < S || threadIdx.x == 32) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -309,7 +298,6 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
     // Every CTA's barriers must exist before a peer arrives on them: all threads arrive on the cluster
     // barrier here; only the hand-over warps, the only ones that touch a peer, wait for it (later).
     if (p.cluster > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    if (threadIdx.x == 0) DK_TRACE(1);
 
     if (warp == DK_PRODUCER) {
         // ---- producer: the warp runs the loop, one elected lane issues each copy ----
@@ -345,9 +333,7 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                 load_weights(i, rb, kt);
                 if (++kt == p.KT) { kt = 0; ++rb; }
             }
-            if (lane == 0) DK_TRACE(2);
             pdl_wait();   // the activations may be written by the preceding kernel
-            if (lane == 0) DK_TRACE(3);
             int kx = kt0;
             for (int i = 0; i < early; ++i) {
                 load_x(i, kx);
@@ -375,7 +361,6 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
         unsigned ph = 0;
         for (int i = 0; i < nt; ++i) {
             mbar_wait(full + s, ph, dead, 5);
-            if (i == 0 && xtid == 0) DK_TRACE(4);
             const unsigned char *raw = rst + (size_t)s * p.raw_bytes;
             uint4 *xw = reinterpret_cast<uint4 *>(xst + (size_t)s * XB);
             if (p.x_dtype == BW_F16) convert_tile<BITS, MT, __half>(raw, xw, xtid);
@@ -404,7 +389,6 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
         pdl_wait();   // outputs, scratch and counters may still be in use by the preceding kernel
         if (p.cluster > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // the peers' barriers are initialised
         const int htid = threadIdx.x - DecWarps<MT>::HANDOVER0 * 32;          // 0..DK_HTHREADS-1
-        if (htid == 0) DK_TRACE(7);
         constexpr int V4 = RED / 4 / DK_HTHREADS;                      // float4 per thread: 2 / 4 / 8
         int rb = rb0, kt = kt0, f = 0;
         for (int i = 0; i < nt; ++f) {
@@ -414,7 +398,6 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             const float4 *r0 = reinterpret_cast<const float4 *>(red + (size_t)b * 2 * RED), *r1 = r0 + RED / 4;
             const int64_t nbase = (int64_t)rb * DK_ROWS;
             mbar_wait(red_full + b, (unsigned)use & 1u, dead, 3);
-            if (htid == 0 && i + len >= nt) DK_TRACE(8);
             float4 v[V4];
 #pragma unroll
             for (int j = 0; j < V4; ++j) {
@@ -512,11 +495,7 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                     flags[3] = nc;
                 }
                 handover_sync();
-                if (flags[1] && i + len >= nt) {
-                    // last CTA to arrive for this row block, and nothing is left to stream: every
-                    // warp of the CTA joins the sum (after the role loops, below)
-                    if (htid == 0) { flags[5] = rb; flags[6] = flags[2]; flags[7] = flags[3]; flags[4] = 1; }
-                } else if (flags[1]) {
+                if (flags[1]) {
                     // last CTA to arrive for this row block: sum the shares in CTA order
                     __threadfence();
                     const int c_lo = flags[2], nc = flags[3];
@@ -542,7 +521,6 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
                 handover_sync();                                 // flags and slots may be reused
             }
             i += len; kt = 0; ++rb;
-            if (htid == 0 && i >= nt) DK_TRACE(9);
         }
     } else {
         // ---- consumers ----
@@ -580,7 +558,6 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
         for (int i = 0; i < nt; ++i) {
             mbar_wait(full + s, ph, dead, 2);               // packed words, scales, zero points
             mbar_wait(xdone + s, ph, dead, 6);              // activations converted
-            if (i == 0 && threadIdx.x == 0) DK_TRACE(5);
             Dequant<BITS> dqa, dqb;
             {
                 const int gtile = ((kt * Geo::TILE_K) >> p.g_shift) & (DK_GBOX - 1);   // the tile's first group inside its box
@@ -646,7 +623,6 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(empty + s);          // this warp is done with the stage
-            if (i == nt - 1 && threadIdx.x == 0) DK_TRACE(6);
             if (++s == S) { s = 0; ph ^= 1u; }
 
             if (kt == p.KT - 1 || i == nt - 1) {
@@ -671,82 +647,15 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             }
         }
     }
-    if (p.cluster == 1) {
-        // The CTA's last share completed its row block: all warps add the shares (CTA order, so the
-        // result does not depend on timing) and store.  Thread = (token, four consecutive rows),
-        // eight loads in flight each: a lone warp group summing at the very end of the kernel is
-        // bound by the latency of its loads.
-        __syncthreads();
-        if (flags[4] && !*dead) {
-            __threadfence();
-            const int rb = flags[5], c_lo = flags[6], nc = flags[7];
-            for (int j = threadIdx.x; j < nc; j += blockDim.x) {
-                const int first_rb = (int)(dec_first_tile(c_lo + j, p.tiles, ctas) / p.KT);
-                slots[j] = 2 * (c_lo + j) + (rb != first_rb ? 1 : 0);
-            }
-            __syncthreads();
-            const int npos = (int)p.M * (DK_ROWS / 4);
-            const bool vec_ok = (p.N & 3) == 0;
-            for (int pos = threadIdx.x; pos < npos; pos += blockDim.x) {
-                const int m = pos >> 5, r4 = pos & 31;
-                const float *src = p.part + (size_t)m * DK_ROWS + (size_t)r4 * 4;
-                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                for (int c = 0; c < nc; c += 8) {
-                    float4 v[8];
-#pragma unroll
-                    for (int u = 0; u < 8; ++u)
-                        v[u] = (c + u < nc) ? __ldcg(reinterpret_cast<const float4 *>(src + (size_t)slots[c + u] * RED))
-                                            : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        if (c + u < nc) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
-                    }
-                }
-                const int64_t n = (int64_t)rb * DK_ROWS + r4 * 4;
-                const float a[4] = {acc.x, acc.y, acc.z, acc.w};
-                if (p.out_dtype == BW_F16) {
-                    __half h[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        h[e] = __float2half_rn(a[e]);                                     // the GEMM's fp16 output rounding
-                        if (p.bias && n + e < p.N) h[e] = __hadd(h[e], p.bias[n + e]);   // separate fp16 bias add
-                    }
-                    __half *dst = reinterpret_cast<__half *>(p.out) + (int64_t)m * p.N + n;
-                    if (vec_ok && n + 3 < p.N) {
-                        *reinterpret_cast<uint2 *>(dst) = make_uint2(h2_as_u32(__halves2half2(h[0], h[1])), h2_as_u32(__halves2half2(h[2], h[3])));
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) if (n + e < p.N) dst[e] = h[e];
-                    }
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        if (n + e >= p.N) continue;
-                        float v = a[e];
-                        if (p.bias) v += __half2float(p.bias[n + e]);
-                        if (p.out_dtype == BW_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[(int64_t)m * p.N + n + e] = __float2bfloat16_rn(v);
-                        else reinterpret_cast<float *>(p.out)[(int64_t)m * p.N + n + e] = v;
-                    }
-                }
-            }
-        }
-    }
-    // A CTA that gave up on a wait may still have copies in flight: give them time to land
-    // before its shared memory is handed to another CTA.
+    // A CTA that gave up on a wait may still have copies in flight, and -- in a cluster -- peers
+    // that have not reached their hand-over yet would store into its shared memory: it lingers for
+    // longer than any peer can spend in its own bounded waits (each gives up after DK_WAIT_LIMIT
+    // polls, ~0.1 s) before its shared memory is handed to another CTA.  (A closing cluster
+    // barrier would make this airtight, but costs every healthy launch of the small shapes
+    // 0.4-0.6 us: the CTAs that have delivered their shares would wait for the one that stores.)
     if (*dead) {
-        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+        for (int i = 0; i < (p.cluster > 1 ? 400000 : 2000); ++i) __nanosleep(1000);
     }
-    // No CTA of a cluster leaves while a peer may still store into its shared memory or arrive on
-    // its barriers (also after a wait ran out: every other wait is bounded, so all CTAs get here).
-    if (p.cluster > 1) {
-        // (only the hand-over warps have waited for the start-up phase of the cluster barrier so far)
-        if (warp < DecWarps<MT>::HANDOVER0) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-    }
-#ifdef BW_TUNING
-    if (p.trace) { __syncthreads(); if (threadIdx.x == 0) DK_TRACE(10); }
-#endif
 }
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -793,13 +702,12 @@ int sm_count() {
 
 }  // namespace
 
-// The slice of g_dec_cnt that calls with this workspace use (shared by the decode and the
-// streaming kernel: calls on one workspace are ordered by their stream).  Calls that may
-// overlap on the GPU already need distinct workspaces, so they also get distinct counters.
-// Slices are handed out per workspace address; when all are taken the least recently used
-// one is reassigned (a call leaves its counters at zero, so a slice can change hands as long
-// as no kernel of its previous owner is still running -- that would take more than
-// DK_CNT_WS workspaces with work in flight on one device at a time).
+// The slice of g_dec_cnt that calls with this workspace use.  Calls that may overlap on the GPU
+// already need distinct workspaces, so they also get distinct counters.  Slices are handed out
+// per workspace address; when all are taken the least recently used one is reassigned (a call
+// leaves its counters at zero, so a slice can change hands as long as no kernel of its previous
+// owner is still running -- that would take more than DK_CNT_WS workspaces with work in flight
+// on one device at a time).
 unsigned *counter_slice(const void *workspace) {
     static std::mutex mu;
     static const void *owner[64][DK_CNT_WS] = {};
@@ -873,26 +781,21 @@ int launch_dec(const DecMaps &maps, DecParams p, cudaStream_t st) {
     if (ctas > DK_MAX_CTAS) ctas = DK_MAX_CTAS;
     if (g_dec.max_ctas > 0) {
         if (ctas > g_dec.max_ctas) ctas = g_dec.max_ctas;
-    } else if (g_dec.max_ctas <= 0 && p.RB <= ctas) {
+    } else if (g_dec.max_ctas == 0 && p.RB <= ctas) {
         // no more row blocks than SMs: give each row block the same number of CTAs, 1, 2, 4 or 8,
         // launched as one thread-block cluster that adds its shares through distributed shared
         // memory (no round trips through L2)
         int per_rb = 1;
         while (per_rb * 2 <= 8 && p.RB * per_rb * 2 <= ctas && per_rb * 2 <= p.KT) per_rb *= 2;
-        // (cutting the tile list into equal ranges over ALL SMs instead -- stream-K through the global
-        // scratch -- was measured slower on the 112-row-block shapes: 16.8 us against 15.1 us)
-        const bool waste = g_dec.max_ctas == -2 && p.RB * per_rb * 10 < ctas * 9 && p.tiles >= 4 * ctas;
-        if (!waste) {
-            ctas = p.RB * per_rb;
-            p.cluster = per_rb;
-            p.cluster_leader = (size_t)(per_rb - 1) * MT * 8 * DK_ROWS * 4 <= 32 * 1024 ? 1 : 0;
-        }
+        ctas = p.RB * per_rb;
+        p.cluster = per_rb;
+        p.cluster_leader = (size_t)(per_rb - 1) * MT * 8 * DK_ROWS * 4 <= 32 * 1024 ? 1 : 0;
     }
     if (ctas > p.tiles) ctas = p.tiles;
     // the first CTA's buffer for the other CTAs' shares, or one [MTOK][128] tile (ranks x slices)
     const size_t cpart_bytes = p.cluster > 1 ? (size_t)(p.cluster_leader ? p.cluster - 1 : 1) * MT * 8 * DK_ROWS * 4 : 0;
     const size_t fixed = 1024 /*alignment slack*/ + (size_t)NRED * 2 * MT * 8 * DK_ROWS * 4 + (3 * DK_MAX_STAGES + 5) * 8 +
-                         32 + DK_MAX_CTAS * 4 + cpart_bytes + 64;
+                         16 + DK_MAX_CTAS * 4 + cpart_bytes + 64;
     const size_t budget = (size_t)(g_dec.smem_kb > 0 ? g_dec.smem_kb : 224) * 1024;
     if (budget < fixed + 2 * stage) return BW_ERR_UNSUPPORTED;
     int stages = (int)((budget - fixed) / stage);
@@ -924,9 +827,6 @@ int launch_dec_mt(const DecMaps &maps, const DecParams &p, int mt, cudaStream_t 
 }  // namespace
 
 void set_decode_tuning(int enabled, int smem_kb, int max_ctas, int pdl) { g_dec = {enabled, smem_kb, max_ctas, pdl}; }
-#ifdef BW_TUNING
-void set_decode_trace(unsigned long long *buf) { g_dec_trace_host = buf; }
-#endif
 
 int decode_device_status() {
     int v = 0, zero = 0;
@@ -987,9 +887,6 @@ int qmatmul_decode(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, 
     p.tiles = p.KT * p.RB;
     p.raw_bytes = mt * 8 * tile_k * (int)dtype_size(x_dtype);
     p.cluster = 1;
-#ifdef BW_TUNING
-    p.trace = g_dec_trace_host;
-#endif
 
     DecMaps maps;
     // packed words [N rows][K/vpi int32]: boxes of 128 rows x 32 words, 128-byte swizzle; scales

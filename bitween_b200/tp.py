@@ -97,24 +97,68 @@ class ColumnParallelQuantizedLinear(nn.Module):
 
 class RowParallelQuantizedLinear(nn.Module):
     """Holds input columns [rank*K/tp, (rank+1)*K/tp) of a QuantizedLinear; the input is the
-    matching slice of the activations and the partial outputs are summed with one all-reduce."""
+    matching slice of the activations and the partial outputs are summed with one all-reduce.
 
-    def __init__(self, shard: QuantizedLinear, group=None):
+    `overlap_chunks` > 1 splits the tokens into that many chunks and runs the all-reduce of chunk
+    i on a second stream while the GEMM of chunk i+1 runs (worth it for prefill, where the
+    all-reduce moves tens of MB; a decode step's 1 MiB all-reduce is bound by latency, not
+    bandwidth, and stays one piece).  `reduce_dtype=torch.float32` makes every rank emit its
+    partial sums unrounded and rounds once after the reduce -- the reference's single fp16
+    rounding -- at twice the bytes on the wire; the default sums fp16 partials (one extra
+    rounding per rank, within the 1e-2 * RMS bar at 8 ranks)."""
+
+    def __init__(self, shard: QuantizedLinear, group=None, overlap_chunks=1, reduce_dtype=None):
         super().__init__()
         self.shard = shard
         self.group = group
+        self.overlap_chunks = int(overlap_chunks)
+        self.reduce_dtype = reduce_dtype
+        self._comm_stream = None
 
     @classmethod
-    def from_full(cls, layer, rank, world, group=None):
-        return cls(shard_quantized_linear(layer, "row", rank, world), group)
+    def from_full(cls, layer, rank, world, group=None, overlap_chunks=1, reduce_dtype=None):
+        return cls(shard_quantized_linear(layer, "row", rank, world), group, overlap_chunks, reduce_dtype)
+
+    def _partial(self, x, out=None):
+        s = self.shard
+        kw = {} if self.reduce_dtype is None else {"out_dtype": self.reduce_dtype}
+        if out is not None:
+            kw["out"] = out
+        return _matmul(x, s.qweight, s.scale, s.zero_point, s.bias, s.bits, s.group_size, **kw)
 
     def forward(self, x_shard):
         s = self.shard
         if x_shard.shape[-1] != s.in_features:
             raise ValueError(f"row-parallel input has {x_shard.shape[-1]} features, this rank holds {s.in_features}")
-        y = _matmul(x_shard, s.qweight, s.scale, s.zero_point, s.bias, s.bits, s.group_size)
-        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
-            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+        distributed = dist.is_initialized() and dist.get_world_size(self.group) > 1
+        x2 = x_shard.reshape(-1, s.in_features)
+        M = x2.shape[0]
+        chunks = min(self.overlap_chunks, M) if distributed and x2.is_cuda else 1
+        if chunks <= 1:
+            y = self._partial(x_shard)
+            if distributed:
+                dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+        else:
+            # GEMM of chunk i+1 (this stream) while chunk i is being reduced (second stream)
+            if self._comm_stream is None:
+                self._comm_stream = torch.cuda.Stream(device=x2.device)
+            dt = self.reduce_dtype or torch.float16
+            y = torch.empty((M, s.out_features), dtype=dt, device=x2.device)
+            main = torch.cuda.current_stream(x2.device)
+            bounds = [M * i // chunks for i in range(chunks + 1)]
+            for i in range(chunks):
+                lo, hi = bounds[i], bounds[i + 1]
+                self._partial(x2[lo:hi], out=y[lo:hi])
+                done = torch.cuda.Event()
+                done.record(main)
+                with torch.cuda.stream(self._comm_stream):
+                    self._comm_stream.wait_event(done)
+                    dist.all_reduce(y[lo:hi], op=dist.ReduceOp.SUM, group=self.group)
+            main.wait_stream(self._comm_stream)
+            y.record_stream(self._comm_stream)
+            y = y.reshape(*x_shard.shape[:-1], s.out_features)
+        if self.reduce_dtype is not None and self.reduce_dtype != torch.float16:
+            y = y.to(torch.float16)
         return y
 
 

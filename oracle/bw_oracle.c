@@ -296,6 +296,17 @@ int bwo_qlinear_grad_input(const void *grad_out, int grad_dtype, int64_t M, int6
     return 0;
 }
 
+/* Sets the number of OpenMP threads of the later calls (launchers such as torchrun export
+ * OMP_NUM_THREADS=1 to their workers; the timed CPU baseline wants all host threads). */
+int bwo_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+    return 0;
+}
+
 int bwo_num_threads(void) {
     int n = 1;
 #ifdef _OPENMP

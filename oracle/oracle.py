@@ -41,8 +41,9 @@ def lib():
         L.bwo_dequantize_module.argtypes = [vp, vp, vp, i64, i64, i32, i32, vp, i32]
         L.bwo_qlinear_forward.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, vp, i32, i32, vp, vp]
         L.bwo_qlinear_grad_input.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, i32, i32, vp]
+        L.bwo_set_num_threads.argtypes = [i32]
         for f in (L.bwo_quantize_rtn, L.bwo_dequantize_rtn, L.bwo_dequantize_module,
-                  L.bwo_qlinear_forward, L.bwo_qlinear_grad_input, L.bwo_num_threads):
+                  L.bwo_qlinear_forward, L.bwo_qlinear_grad_input, L.bwo_num_threads, L.bwo_set_num_threads):
             f.restype = ctypes.c_int
         _lib = L
     return _lib
@@ -50,6 +51,11 @@ def lib():
 
 def num_threads():
     return int(lib().bwo_num_threads())
+
+
+def set_num_threads(n):
+    """OpenMP threads used by the later calls (overrides OMP_NUM_THREADS of the environment)."""
+    lib().bwo_set_num_threads(int(n))
 
 
 # ---- 16-bit float helpers (bit patterns in uint16) ---------------------------------
