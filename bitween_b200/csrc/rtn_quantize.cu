@@ -87,6 +87,29 @@ template <> __device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4 
     }
 }
 
+// min / max of the elements of one 16-byte chunk (NaNs dropped, as fminf / fmaxf do): on packed
+// 16-bit pairs where the input is 16-bit -- min and max are exact in any format and cost one
+// instruction per two elements there.
+template <typename T> __device__ __forceinline__ void lane_minmax(const uint4 &raw, const float (&v)[Elems16<T>::V], float &mn, float &mx);
+template <> __device__ __forceinline__ void lane_minmax<float>(const uint4 &, const float (&v)[4], float &mn, float &mx) {
+    mn = fminf(fminf(v[0], v[1]), fminf(v[2], v[3]));
+    mx = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
+}
+template <> __device__ __forceinline__ void lane_minmax<__half>(const uint4 &raw, const float (&)[8], float &mn, float &mx) {
+    const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+    const __half2 lo = __hmin2(__hmin2(h[0], h[1]), __hmin2(h[2], h[3]));
+    const __half2 hi = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+    mn = fminf(__low2float(lo), __high2float(lo));
+    mx = fmaxf(__low2float(hi), __high2float(hi));
+}
+template <> __device__ __forceinline__ void lane_minmax<__nv_bfloat16>(const uint4 &raw, const float (&)[8], float &mn, float &mx) {
+    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+    const __nv_bfloat162 lo = __hmin2(__hmin2(h[0], h[1]), __hmin2(h[2], h[3]));
+    const __nv_bfloat162 hi = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+    mn = fminf(__low2float(lo), __high2float(lo));
+    mx = fmaxf(__low2float(hi), __high2float(hi));
+}
+
 template <typename ZT> __device__ __forceinline__ void store_zp(ZT *p, int32_t z);
 template <> __device__ __forceinline__ void store_zp<int32_t>(int32_t *p, int32_t z) { *p = z; }
 template <> __device__ __forceinline__ void store_zp<__half>(__half *p, int32_t z) { *p = __int2half_rn(z); }
@@ -139,10 +162,41 @@ __device__ __forceinline__ float div_by_recip(float v, float s, float r) {
     return __fmaf_rn(__fmaf_rn(-s, q1, v), r, q1);
 }
 
+// The same division for two elements at a time with the packed fp32 instructions of sm_100
+// (fma.rn.f32x2 / mul.rn.f32x2 / add.rn.f32x2: each lane of the pair is an IEEE operation with
+// round-to-nearest-even, so the sequence above stays exact; one issue slot instead of two).
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n .reg .b64 ra, rb, rc, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mov.b64 rc, {%6, %7};\n"
+        " fma.rn.f32x2 rd, ra, rb, rc;\n mov.b64 {%0, %1}, rd;\n}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n .reg .b64 ra, rb, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n"
+        " mul.rn.f32x2 rd, ra, rb;\n mov.b64 {%0, %1}, rd;\n}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n .reg .b64 ra, rb, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n"
+        " add.rn.f32x2 rd, ra, rb;\n mov.b64 {%0, %1}, rd;\n}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+__device__ __forceinline__ float2 div_by_recip2(float2 v, float s, float r) {
+    const float2 s2 = make_float2(-s, -s), r2 = make_float2(r, r);
+    const float2 q0 = fmul2(v, r2);
+    const float2 q1 = ffma2(ffma2(s2, q0, v), r2, q0);
+    return ffma2(ffma2(s2, q1, v), r2, q1);
+}
+
 // One 16-byte chunk per lane: group min/max over the lane segment, group parameters, codes,
 // packed words and the group's scale / zero-point.  `c` is the global chunk index of this lane.
 template <typename T, bool NATIVE, int BITS, typename ST, typename ZT>
-__device__ __forceinline__ void rtn_slot(float (&v)[Elems16<T>::V], int64_t c, bool in_range, int lane, int cpg,
+__device__ __forceinline__ void rtn_slot(const uint4 &raw, int64_t c, bool in_range, int lane, int cpg,
                                          int cpg_log2, uint32_t seg_mask, float floor_s,
                                          int32_t *__restrict__ qweight, ST *__restrict__ scale,
                                          ZT *__restrict__ zp) {
@@ -151,17 +205,17 @@ __device__ __forceinline__ void rtn_slot(float (&v)[Elems16<T>::V], int64_t c, b
     constexpr float QMAX = (float)((1 << BITS) - 1);
     constexpr float MAGIC = 12582912.0f;                 // 1.5 * 2^23
     constexpr uint32_t MAGIC_BITS = 0x4B400000u;
-    float mn = v[0], mx = v[0];
-    // NaN/Inf detector on the (otherwise idle) FMA pipe: a sum is NaN or Inf as soon as one
-    // addend is; a sum of finite values that overflows only sends the group down the slow,
-    // still exact, path.  fminf/fmaxf drop NaNs, so they cannot serve as the detector.
-    float sum = v[0];
+    float v[V];
+    unpack16<T>(raw, v);
+    float mn, mx;
+    lane_minmax<T>(raw, v, mn, mx);
+    // NaN/Inf detector on the FMA pipe: a sum is NaN or Inf as soon as one addend is; a sum of
+    // finite values that overflows only sends the group down the slow, still exact, path.
+    // fminf/fmaxf drop NaNs, so they cannot serve as the detector.
+    float2 sum2 = make_float2(v[0], v[1]);
 #pragma unroll
-    for (int j = 1; j < V; ++j) {
-        mn = fminf(mn, v[j]);
-        mx = fmaxf(mx, v[j]);
-        sum = __fadd_rn(sum, v[j]);
-    }
+    for (int j = 2; j < V; j += 2) sum2 = fadd2(sum2, make_float2(v[j], v[j + 1]));
+    const float sum = __fadd_rn(sum2.x, sum2.y);
     for (int off = cpg >> 1; off > 0; off >>= 1) {
         mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
@@ -169,6 +223,8 @@ __device__ __forceinline__ void rtn_slot(float (&v)[Elems16<T>::V], int64_t c, b
     // bad: a NaN/Inf in this lane's elements, or a weight beyond +-2^40 in the group
     const bool bad = !(fabsf(sum) <= 3.0e38f) || !(mn >= -1.0995116e12f) || !(mx <= 1.0995116e12f);
     const bool group_bad = (__ballot_sync(0xffffffffu, bad) & seg_mask) != 0u;
+    // (all lanes of the warp are together here; the vote is used by the fast path below)
+    const bool lower_clamp = !NATIVE && __any_sync(0xffffffffu, !(mn <= 0.0f && mx >= 0.0f));
     float s, zf; int32_t zi;
     uint32_t words[V >= VPI ? V / VPI : 1];
     bool fast = !group_bad;
@@ -188,21 +244,43 @@ __device__ __forceinline__ void rtn_slot(float (&v)[Elems16<T>::V], int64_t c, b
     }
     if (fast) {
         const int pos0 = (V >= VPI) ? 0 : (lane & (VPI / V - 1)) * V;
+        // When a group's range contains zero, zero_point = round(-min/scale) is not clamped and
+        // w/scale + zero_point >= -1/2 for every element (RN(min/scale) = -RN(-min/scale) and the
+        // division is monotonic), which the magic-number rounding below turns into code 0: the
+        // lower clamp does nothing.  Weights almost always look like that, so the whole warp
+        // votes (above, where all lanes are still together) and skips it (one instruction per element).
 #pragma unroll
         for (int wi = 0; wi < (V >= VPI ? V / VPI : 1); ++wi) {
             // word = sum_i code_i * 2^(pos_i*bits); the codes arrive as MAGIC_BITS + code_i, so
             // one integer multiply-add per element accumulates them and the constant
             // MAGIC_BITS * sum_i 2^(pos_i*bits) is removed once at the end (mod 2^32).
             uint32_t acc = 0, bias = 0;
+            if constexpr (!NATIVE) {
+                // fp32 arithmetic: two elements per packed instruction
 #pragma unroll
-            for (int i = 0; i < (V >= VPI ? VPI : V); ++i) {
-                const float x = v[wi * VPI + i];
-                float t = rnd<T, NATIVE>(div_by_recip(x, s, r));
-                t = rnd<T, NATIVE>(__fadd_rn(t, zf));
-                t = fminf(fmaxf(t, 0.0f), QMAX);
-                const uint32_t mul = 1u << ((pos0 + i) * BITS);
-                acc += __float_as_uint(__fadd_rn(t, MAGIC)) * mul;
-                bias += MAGIC_BITS * mul;
+                for (int i = 0; i < (V >= VPI ? VPI : V); i += 2) {
+                    float2 t = div_by_recip2(make_float2(v[wi * VPI + i], v[wi * VPI + i + 1]), s, r);
+                    t = fadd2(t, make_float2(zf, zf));
+                    if (lower_clamp) { t.x = fmaxf(t.x, 0.0f); t.y = fmaxf(t.y, 0.0f); }
+                    t.x = fminf(t.x, QMAX);
+                    t.y = fminf(t.y, QMAX);
+                    t = fadd2(t, make_float2(MAGIC, MAGIC));
+                    const uint32_t mul0 = 1u << ((pos0 + i) * BITS), mul1 = 1u << ((pos0 + i + 1) * BITS);
+                    acc += __float_as_uint(t.x) * mul0;
+                    acc += __float_as_uint(t.y) * mul1;
+                    bias += MAGIC_BITS * mul0 + MAGIC_BITS * mul1;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < (V >= VPI ? VPI : V); ++i) {
+                    const float x = v[wi * VPI + i];
+                    float t = rnd<T, NATIVE>(div_by_recip(x, s, r));
+                    t = rnd<T, NATIVE>(__fadd_rn(t, zf));
+                    t = fminf(fmaxf(t, 0.0f), QMAX);
+                    const uint32_t mul = 1u << ((pos0 + i) * BITS);
+                    acc += __float_as_uint(__fadd_rn(t, MAGIC)) * mul;
+                    bias += MAGIC_BITS * mul;
+                }
             }
             words[wi] = acc - bias;
         }
@@ -263,20 +341,16 @@ rtn_quantize_pack_kernel(const T *__restrict__ w, int64_t total_chunks, int cpg_
     const int64_t c0 = warp * (32 * L) + lane;
     const int cpg = 1 << cpg_log2;
     const uint32_t seg_mask = (cpg == 32) ? 0xffffffffu : (((1u << cpg) - 1u) << (lane & ~(cpg - 1)));
-    float v[L][V];
+    uint4 raw[L];
 #pragma unroll
     for (int l = 0; l < L; ++l) {
         const int64_t c = c0 + l * 32;
-        if (c < total_chunks) load16<T>(w + c * V, v[l]);
-        else {
-#pragma unroll
-            for (int j = 0; j < V; ++j) v[l][j] = 0.0f;
-        }
+        raw[l] = (c < total_chunks) ? __ldcs(reinterpret_cast<const uint4 *>(w + c * V)) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int l = 0; l < L; ++l) {
         const int64_t c = c0 + l * 32;
-        rtn_slot<T, NATIVE, BITS, ST, ZT>(v[l], c, c < total_chunks, lane, cpg, cpg_log2, seg_mask, floor_s,
+        rtn_slot<T, NATIVE, BITS, ST, ZT>(raw[l], c, c < total_chunks, lane, cpg, cpg_log2, seg_mask, floor_s,
                                           qweight, scale, zp);
     }
 }
@@ -317,20 +391,16 @@ rtn_quantize_pack_batch_kernel(const RtnBatchEntry *__restrict__ table, int njob
     const int64_t c0 = warp * (32 * L) + lane;
     const int cpg = 1 << cpg_log2;
     const uint32_t seg_mask = (cpg == 32) ? 0xffffffffu : (((1u << cpg) - 1u) << (lane & ~(cpg - 1)));
-    float v[L][V];
+    uint4 raw[L];
 #pragma unroll
     for (int l = 0; l < L; ++l) {
         const int64_t c = c0 + l * 32;
-        if (c < e.chunks) load16<T>(w + c * V, v[l]);
-        else {
-#pragma unroll
-            for (int j = 0; j < V; ++j) v[l][j] = 0.0f;
-        }
+        raw[l] = (c < e.chunks) ? __ldcs(reinterpret_cast<const uint4 *>(w + c * V)) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int l = 0; l < L; ++l) {
         const int64_t c = c0 + l * 32;
-        rtn_slot<T, NATIVE, BITS, ST, ZT>(v[l], c, c < e.chunks, lane, cpg, cpg_log2, seg_mask, floor_s, e.q,
+        rtn_slot<T, NATIVE, BITS, ST, ZT>(raw[l], c, c < e.chunks, lane, cpg, cpg_log2, seg_mask, floor_s, e.q,
                                           reinterpret_cast<ST *>(e.scale), reinterpret_cast<ZT *>(e.zp));
     }
 }
@@ -413,15 +483,11 @@ rtn_quantize_pack_stream_kernel(const T *__restrict__ w, int64_t total_chunks, i
         }
         const int64_t first = tile_of(it) * RTN_TILE_CHUNKS;
         const uint4 *tile = ring + st * RTN_TILE_CHUNKS;
-        float v[RTN_L][V];
+        uint4 v[RTN_L];
 #pragma unroll
         for (int l = 0; l < RTN_L; ++l) {
             const int cl = (tid >> 5) * (32 * RTN_L) + l * 32 + lane;
-            if (first + cl < total_chunks) unpack16<T>(tile[cl], v[l]);
-            else {
-#pragma unroll
-                for (int j = 0; j < V; ++j) v[l][j] = 0.0f;
-            }
+            v[l] = (first + cl < total_chunks) ? tile[cl] : make_uint4(0, 0, 0, 0);
         }
         // generic-proxy reads of the stage are ordered before the bulk copy that refills it
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -507,7 +573,7 @@ int launch_typed(const T *w, int64_t N, int64_t K, int g, int32_t *q, ST *scale,
                  cudaStream_t st) {
     constexpr int V = Elems16<T>::V;
     constexpr int VPI = 32 / BITS;
-    constexpr int L = (sizeof(T) == 4) ? 4 : 2;
+    constexpr int L = 4;
     const int64_t total = N * K;
     if (total == 0) return BW_OK;
     int cpg_log2 = -1;
@@ -602,6 +668,10 @@ __global__ void div_check_kernel(uint64_t n, uint64_t seed, unsigned long long *
         const float s = qconst != 0.0f ? qconst : __uint_as_float((uint32_t)es << 23 | ms);   // Qmax divisors too
         const float a = div_by_recip(v, s, __frcp_rn(s)), b = __fdiv_rn(v, s);
         if (__float_as_uint(a) != __float_as_uint(b)) ++bad;
+        // the packed form, with a second numerator in the other lane
+        const float v2 = -v * 0.75f;
+        const float2 p = div_by_recip2(make_float2(v, v2), s, __frcp_rn(s));
+        if (__float_as_uint(p.x) != __float_as_uint(b) || __float_as_uint(p.y) != __float_as_uint(__fdiv_rn(v2, s))) ++bad;
     }
     if (bad) atomicAdd(mismatches, bad);
 }
@@ -650,7 +720,7 @@ size_t rtn_batch_table_bytes(int njobs) { return njobs > 0 ? (size_t)njobs * siz
 // words), else one launch per matrix.  `table_dev` receives the job table (one asynchronous copy).
 int rtn_quantize_pack_batch(const bw_rtn_job *jobs, int njobs, int w_dtype, int bits, int g, int scale_dtype,
                             int zp_dtype, unsigned flags, void *table_dev, cudaStream_t st) {
-    const int v = 16 / (int)dtype_size(w_dtype), lpt = w_dtype == BW_F32 ? 4 : 2;
+    const int v = 16 / (int)dtype_size(w_dtype), lpt = 4;
     bool fast = table_dev != nullptr && g % v == 0 && (g / v) <= 32 && ((g / v) & (g / v - 1)) == 0 && njobs <= 4096;
     for (int j = 0; j < njobs && fast; ++j)
         fast = aligned_to(jobs[j].w, 16) && aligned_to(jobs[j].qweight, 8);
