@@ -9,6 +9,8 @@ namespace bw {
 
 static thread_local char g_cuda_error[256] = "";
 static thread_local const char *g_last_kernel = "";
+static thread_local Epilogue g_epilogue = {BW_ACT_NONE, nullptr};
+Epilogue current_epilogue() { return g_epilogue; }
 
 int record_cuda_error(cudaError_t e, const char *where) {
     snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s (%s)", where, cudaGetErrorName(e),
@@ -223,6 +225,21 @@ int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
                int bits, int group_size, void *workspace, size_t workspace_bytes, void *stream) {
     return qmatmul_dispatch(x, x_dtype, M, N, K, qweight, scale, zero_point, bias, out, out_dtype, bits,
                             group_size, workspace, workspace_bytes, stream, true, true);
+}
+
+int bw_qmatmul_fused(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *qweight,
+                     const void *scale, const void *zero_point, const void *bias, void *out, int out_dtype,
+                     int bits, int group_size, const bw_epilogue *ep, void *workspace, size_t workspace_bytes,
+                     void *stream) {
+    if (ep) {
+        if (ep->activation != BW_ACT_NONE && ep->activation != BW_ACT_RELU) return BW_ERR_UNSUPPORTED;
+        if (!aligned_to(ep->residual, 2)) return BW_ERR_ALIGN;
+        g_epilogue = {ep->activation, reinterpret_cast<const __half *>(ep->residual)};
+    }
+    const int rc = qmatmul_dispatch(x, x_dtype, M, N, K, qweight, scale, zero_point, bias, out, out_dtype, bits,
+                                    group_size, workspace, workspace_bytes, stream, true, true);
+    g_epilogue = {BW_ACT_NONE, nullptr};
+    return rc;
 }
 
 int bw_qmatmul_noalloc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K,

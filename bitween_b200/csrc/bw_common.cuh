@@ -59,4 +59,34 @@ template <> __device__ __forceinline__ float from_f32<float>(float v) { return v
 template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// ---- output epilogue shared by the quantized-matmul kernels ------------------------------
+// What follows the linear in a decoder block, done on the value before it leaves the SM instead
+// of by one more elementwise kernel each (the reference adds even the bias with a separate
+// kernel, bitween/modules.py:100-101): activation (ReLU, the OPT feed-forward) and residual add.
+// fp16 outputs reproduce the eager op-by-op result: fp16(acc), + bias, relu, + residual, each
+// rounded to fp16 like the separate torch ops would.
+struct Epilogue {
+    int act;                  // BW_ACT_NONE | BW_ACT_RELU
+    const __half *residual;   // [M, N] fp16, added last, or null
+};
+// The epilogue of the bw_qmatmul_fused call in progress on this thread (none otherwise).
+Epilogue current_epilogue();
+
+__device__ __forceinline__ void store_output(void *out, int out_dtype, int64_t idx, float v, bool has_bias, __half bias,
+                                             const Epilogue &ep) {
+    if (out_dtype == BW_F16) {
+        __half c = __float2half_rn(v);                       // the GEMM's fp16 output rounding
+        if (has_bias) c = __hadd(c, bias);                   // separate fp16 bias add
+        if (ep.act == BW_ACT_RELU) c = __hmax(c, __float2half(0.0f));
+        if (ep.residual) c = __hadd(c, ep.residual[idx]);
+        reinterpret_cast<__half *>(out)[idx] = c;
+    } else {
+        if (has_bias) v += __half2float(bias);
+        if (ep.act == BW_ACT_RELU) v = fmaxf(v, 0.0f);
+        if (ep.residual) v += __half2float(ep.residual[idx]);
+        if (out_dtype == BW_BF16) reinterpret_cast<__nv_bfloat16 *>(out)[idx] = __float2bfloat16_rn(v);
+        else reinterpret_cast<float *>(out)[idx] = v;
+    }
+}
+
 }  // namespace bw

@@ -240,11 +240,13 @@ __device__ __forceinline__ int dec_cta_of(int64_t tile, int64_t tiles, int64_t c
     return (int)(((tile + 1) * ctas - 1) / tiles);
 }
 
-template <int BITS, int MT>
+// EPI: the output stage applies an activation / residual add (bw_qmatmul_fused); a separate
+// instantiation, so that the plain kernel's code is not touched by it.
+template <int BITS, int MT, bool EPI>
 __global__ void __launch_bounds__(DecWarps<MT>::THREADS, 1)
 qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap s_map,
                   const __grid_constant__ CUtensorMap z_map, const __grid_constant__ CUtensorMap x_map,
-                  const DecParams p) {
+                  const DecParams p, const Epilogue ep) {
     using Geo = DecGeom<BITS>;
     constexpr int MTOK = MT * 8;
     constexpr int XB = DecX<BITS, MT>::BYTES;
@@ -376,7 +378,9 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
         // hands: whole row blocks are stored, shares go to the scratch and the last CTA to
         // arrive for a row block sums them in CTA order ----
         auto store_out = [&](int64_t m, int64_t n, float v) {
-            if (p.out_dtype == BW_F16) {
+            if constexpr (EPI) {
+                store_output(p.out, p.out_dtype, m * p.N + n, v, p.bias != nullptr, p.bias ? p.bias[n] : __half(), ep);
+            } else if (p.out_dtype == BW_F16) {
                 __half c = __float2half_rn(v);                       // the GEMM's fp16 output rounding
                 if (p.bias) c = __hadd(c, p.bias[n]);                // separate fp16 bias add
                 reinterpret_cast<__half *>(p.out)[m * p.N + n] = c;
@@ -770,9 +774,9 @@ int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, int cluster, cudaS
 
 struct DecMaps { CUtensorMap w, s, z, x; };
 
-template <int BITS, int MT>
-int launch_dec(const DecMaps &maps, DecParams p, cudaStream_t st) {
-    auto kern = qmm_decode_kernel<BITS, MT>;
+template <int BITS, int MT, bool EPI>
+int launch_dec(const DecMaps &maps, DecParams p, const Epilogue &ep, cudaStream_t st) {
+    auto kern = qmm_decode_kernel<BITS, MT, EPI>;
     constexpr size_t XB = DecX<BITS, MT>::BYTES;
     constexpr int NRED = MT == 4 ? 1 : 2;
     const size_t stage = DK_W_BYTES + 2 * DK_C_BYTES + XB + (size_t)p.raw_bytes;
@@ -812,15 +816,23 @@ int launch_dec(const DecMaps &maps, DecParams p, cudaStream_t st) {
         BW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
-    return launch_pdl(kern, dim3((unsigned)ctas), dim3(DecWarps<MT>::THREADS), smem, p.cluster, st, maps.w, maps.s, maps.z, maps.x, p);
+    return launch_pdl(kern, dim3((unsigned)ctas), dim3(DecWarps<MT>::THREADS), smem, p.cluster, st, maps.w, maps.s, maps.z, maps.x, p, ep);
 }
 
 template <int BITS>
 int launch_dec_mt(const DecMaps &maps, const DecParams &p, int mt, cudaStream_t st) {
+    const Epilogue ep = current_epilogue();
+    if (ep.act != BW_ACT_NONE || ep.residual) {
+        switch (mt) {
+            case 1: return launch_dec<BITS, 1, true>(maps, p, ep, st);
+            case 2: return launch_dec<BITS, 2, true>(maps, p, ep, st);
+            default: return launch_dec<BITS, 4, true>(maps, p, ep, st);
+        }
+    }
     switch (mt) {
-        case 1: return launch_dec<BITS, 1>(maps, p, st);
-        case 2: return launch_dec<BITS, 2>(maps, p, st);
-        default: return launch_dec<BITS, 4>(maps, p, st);
+        case 1: return launch_dec<BITS, 1, false>(maps, p, ep, st);
+        case 2: return launch_dec<BITS, 2, false>(maps, p, ep, st);
+        default: return launch_dec<BITS, 4, false>(maps, p, ep, st);
     }
 }
 

@@ -66,6 +66,7 @@ struct SmallMParams {
     int chunks_per_cta;   // k-chunks handled by one CTA of the split-K cluster
     int gblock;           // k-chunks whose activations and group constants are staged at once (multiple of PF)
     int splits;           // cluster size along y
+    Epilogue ep;          // activation / residual add on the way out
 };
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -361,15 +362,7 @@ qmm_smallm_kernel(const SmallMParams p) {
 
     // ---- epilogue ---------------------------------------------------------------------
     auto store_out = [&](int64_t m, int64_t n, float v) {
-        if (p.out_dtype == BW_F16) {
-            __half c = __float2half_rn(v);                       // the GEMM's fp16 output rounding
-            if (p.bias) c = __hadd(c, p.bias[n]);                // separate fp16 bias add
-            reinterpret_cast<__half *>(p.out)[m * p.N + n] = c;
-        } else {
-            if (p.bias) v += __half2float(p.bias[n]);
-            if (p.out_dtype == BW_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[m * p.N + n] = __float2bfloat16_rn(v);
-            else reinterpret_cast<float *>(p.out)[m * p.N + n] = v;
-        }
+        store_output(p.out, p.out_dtype, m * p.N + n, v, p.bias != nullptr, p.bias ? p.bias[n] : __half(), p.ep);
     };
 
     if (p.splits == 1) {
@@ -455,17 +448,8 @@ qmm_general_kernel(const SmallMParams p, int g, int64_t m0, int mcount) {
         for (int off = 16; off > 0; off >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
     if (lane == 0) {
         for (int j = 0; j < mcount; ++j) {
-            float v = acc[j];
             const int64_t m = m0 + j;
-            if (p.out_dtype == BW_F16) {
-                __half c = __float2half_rn(v);
-                if (p.bias) c = __hadd(c, p.bias[n]);
-                reinterpret_cast<__half *>(p.out)[m * p.N + n] = c;
-            } else {
-                if (p.bias) v += __half2float(p.bias[n]);
-                if (p.out_dtype == BW_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[m * p.N + n] = __float2bfloat16_rn(v);
-                else reinterpret_cast<float *>(p.out)[m * p.N + n] = v;
-            }
+            store_output(p.out, p.out_dtype, m * p.N + n, acc[j], p.bias != nullptr, p.bias ? p.bias[n] : __half(), p.ep);
         }
     }
 }
@@ -648,6 +632,7 @@ int qmatmul_smallm(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, 
     SmallMParams p = {};
     p.x = x; p.q = q; p.scale = scale; p.zp = zp; p.bias = bias; p.out = out;
     p.M = M; p.N = N; p.K = K; p.x_dtype = x_dtype; p.out_dtype = out_dtype;
+    p.ep = current_epilogue();
     p.G = (int)(K / g);
     p.words_per_row = (int)(K / (32 / bits));
     if (!smallm_fast_path_ok(x, x_dtype, K, q, bits, g)) {

@@ -197,6 +197,7 @@ struct TcParams {
     int splits;         // split-K factor = cluster size along grid z
     int kper;           // k-stages per split
     int x_is_bf16;      // always 0: kind::f16 MMAs take both operands in one 16-bit format
+    Epilogue ep;        // activation / residual add on the way out
 };
 
 // Words of one row for one 64-k stage, as 16-byte vectors, and the natural-order expansion.
@@ -433,15 +434,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
         const int nblk = bn < 32 ? 1 : bn / 32, per = (nblk + TC_DQ_GROUPS - 1) / TC_DQ_GROUPS;
         const __half bias_h = (p.bias && n_ok) ? p.bias[n] : __float2half(0.0f);
         auto store_out = [&](int64_t m, float v) {
-            if (p.out_dtype == BW_F16) {
-                __half c = __float2half_rn(v);
-                if (p.bias) c = __hadd(c, bias_h);
-                reinterpret_cast<__half *>(p.out)[m * p.N + n] = c;
-            } else {
-                if (p.bias) v += __half2float(bias_h);
-                if (p.out_dtype == BW_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[m * p.N + n] = __float2bfloat16_rn(v);
-                else reinterpret_cast<float *>(p.out)[m * p.N + n] = v;
-            }
+            store_output(p.out, p.out_dtype, m * p.N + n, v, p.bias != nullptr, bias_h, p.ep);
         };
         if (p.splits == 1) {
             if (acc_ok) {
@@ -486,17 +479,8 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
                 float v = 0.0f;
                 for (int q = 0; q < nranks; ++q) v += cluster.map_shared_rank(red, q)[c * TC_BM + row];
                 const int64_t m = (int64_t)m0 + c;
-                if (n < p.N && m < p.M) {
-                    if (p.out_dtype == BW_F16) {
-                        __half h = __float2half_rn(v);
-                        if (p.bias) h = __hadd(h, bias_h);
-                        reinterpret_cast<__half *>(p.out)[m * p.N + n] = h;
-                    } else {
-                        if (p.bias) v += __half2float(bias_h);
-                        if (p.out_dtype == BW_BF16) reinterpret_cast<__nv_bfloat16 *>(p.out)[m * p.N + n] = __float2bfloat16_rn(v);
-                        else reinterpret_cast<float *>(p.out)[m * p.N + n] = v;
-                    }
-                }
+                if (n < p.N && m < p.M)
+                    store_output(p.out, p.out_dtype, m * p.N + n, v, p.bias != nullptr, bias_h, p.ep);
             }
         }
         cluster.sync();   // keep shared memory alive until every peer has read it
@@ -656,6 +640,7 @@ int qmatmul_tc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
     p.k_stages = (int)((K + TC_BK - 1) / TC_BK);
     p.bn = M > 128 ? 256 : (M > 64 ? 128 : (M > 32 ? 64 : (M > 16 ? 32 : 16)));
     p.x_is_bf16 = 0;
+    p.ep = current_epilogue();
 
     CUtensorMap map;
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};

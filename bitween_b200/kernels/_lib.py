@@ -38,6 +38,14 @@ def dtype_code(dt):
         raise TypeError(f"bitween_b200: unsupported dtype {dt}") from None
 
 
+ACT_NONE, ACT_RELU = 0, 1
+
+
+class Epilogue(ctypes.Structure):
+    """bw_epilogue of include/bitween_b200.h."""
+    _fields_ = [("activation", ctypes.c_int), ("residual", ctypes.c_void_p)]
+
+
 class RtnJob(ctypes.Structure):
     """bw_rtn_job of include/bitween_b200.h."""
     _fields_ = [("w", ctypes.c_void_p), ("qweight", ctypes.c_void_p), ("scale", ctypes.c_void_p),
@@ -60,6 +68,8 @@ def _declare(L):
     L.bw_qmatmul_workspace_bytes_for.restype = sz
     L.bw_qmatmul.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, vp, vp, i32, i32, i32, vp, sz, vp]
     L.bw_qmatmul.restype = i32
+    L.bw_qmatmul_fused.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, vp, vp, i32, i32, i32, ctypes.POINTER(Epilogue), vp, sz, vp]
+    L.bw_qmatmul_fused.restype = i32
     L.bw_qmatmul_noalloc.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, vp, vp, i32, i32, i32, vp]
     L.bw_qmatmul_noalloc.restype = i32
     L.bw_qmatmul_noalloc_max_scratch_bytes.argtypes = []

@@ -21,11 +21,15 @@ def _as_half(t, name):
 
 
 def quantized_matmul_cuda(x, qweight, scale, zero_point, bias, bits, group_size, out_dtype=None,
-                          out=None):
+                          out=None, activation=None, residual=None):
     """x [..., K] (fp16/bf16/fp32, cast to fp16 as bitween/modules.py:74 does) times the packed
     weight [N, K*bits/32] with fp16 per-group scale / zero_point [N, K/group_size] and an
     optional fp16 bias [N].  Returns fp16 [..., N] exactly as the reference forward does
     (bitween/modules.py:106); `out_dtype` (bf16 / fp32) is an extension of this library.
+
+    `activation="relu"` and `residual` (fp16 [..., N], added last) fuse what follows the linear in
+    a decoder block into the kernel's output stage (C ABI: bw_qmatmul_fused): the result equals
+    `torch.relu(linear) + residual` computed op by op in fp16.
     """
     if bits not in (2, 4, 8):
         raise ValueError("Only 2, 4, or 8 bits are supported.")
@@ -66,15 +70,27 @@ def quantized_matmul_cuda(x, qweight, scale, zero_point, bias, bits, group_size,
     else:
         if out.dtype != out_dtype or tuple(out.shape) != (M, N) or not out.is_contiguous() or out.device != dev:
             raise ValueError("`out` must be a contiguous [M, N] tensor of out_dtype on x's device")
+    if activation not in (None, "relu"):
+        raise ValueError("activation must be None or 'relu'")
+    ep = None
+    if activation is not None or residual is not None:
+        if residual is not None:
+            _lib.require_cuda(residual, "residual")
+            if residual.dtype != torch.float16 or residual.numel() != M * N or residual.device != dev:
+                raise ValueError("`residual` must be an fp16 tensor of the output's shape on x's device")
+            residual = residual.contiguous()
+        ep = _lib.Epilogue(_lib.ACT_RELU if activation == "relu" else _lib.ACT_NONE,
+                           None if residual is None else residual.data_ptr())
     L = _lib.lib()
     with torch.cuda.device(dev):
         ws_bytes = L.bw_qmatmul_workspace_bytes_for(M, N, K, bits, group_size, _lib.dtype_code(x2.dtype),
                                                     16 if x2.data_ptr() % 16 == 0 else 2)
         ws = _lib.workspace(dev, ws_bytes)
-        rc = L.bw_qmatmul(_lib.ptr(x2), _lib.dtype_code(x2.dtype), M, N, K, _lib.ptr(qweight),
-                          _lib.ptr(scale), _lib.ptr(zero_point), _lib.ptr(bias), _lib.ptr(out),
-                          _lib.dtype_code(out_dtype), bits, group_size, _lib.ptr(ws),
-                          0 if ws is None else ws.numel(), _lib.stream_ptr(dev))
+        args = (_lib.ptr(x2), _lib.dtype_code(x2.dtype), M, N, K, _lib.ptr(qweight),
+                _lib.ptr(scale), _lib.ptr(zero_point), _lib.ptr(bias), _lib.ptr(out),
+                _lib.dtype_code(out_dtype), bits, group_size)
+        tail = (_lib.ptr(ws), 0 if ws is None else ws.numel(), _lib.stream_ptr(dev))
+        rc = L.bw_qmatmul(*args, *tail) if ep is None else L.bw_qmatmul_fused(*args, ep, *tail)
     _lib.check(rc)
     return out.reshape(*x.shape[:-1], N)
 

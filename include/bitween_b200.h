@@ -171,6 +171,30 @@ BW_API int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t 
                void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * bw_qmatmul with the operations that follow the linear in a decoder block fused into the
+ * kernels' output stage: activation and residual add.  The reference runs them -- and even the
+ * bias add (bitween/modules.py:100-101) -- as separate elementwise kernels over [M, N]; the
+ * block structure they come from is the one bitween/gradual/utils.py:292-392 walks (OPT:
+ * fc1 -> ReLU -> fc2 -> + residual).
+ *   out = act( fp16(fp16(acc) + bias) ) + residual      (each step rounded to fp16 for BW_F16 out,
+ *                                                         like the separate torch ops; fp32 math
+ *                                                         with one final rounding otherwise)
+ *   ep->activation  BW_ACT_NONE | BW_ACT_RELU
+ *   ep->residual    [M,N] fp16 or NULL; may alias `out`
+ * ep == NULL is bw_qmatmul.
+ */
+#define BW_ACT_NONE 0
+#define BW_ACT_RELU 1
+typedef struct {
+    int activation;
+    const void *residual;
+} bw_epilogue;
+BW_API int bw_qmatmul_fused(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K,
+                     const int32_t *qweight, const void *scale, const void *zero_point,
+                     const void *bias, void *out, int out_dtype, int bits, int group_size,
+                     const bw_epilogue *ep, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
  * bw_qmatmul for callers that cannot allocate device memory.  (No counterpart in the
  * reference: its forward allocates a temporary fp16 [N,K] on every call.)
  *

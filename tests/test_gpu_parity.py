@@ -520,3 +520,35 @@ def test_rtn_batched_call_equals_single_calls_bit_for_bit():
                 q1, s1, z1 = quantize_rtn_to_module_buffers(w, bits, g)
                 assert torch.equal(q, q1) and torch.equal(s, s1) and torch.equal(z, z1), (dt, bits, g, tuple(w.shape))
     assert _lib.lib().bw_device_status() == 0
+
+
+@pytest.mark.parametrize("case", [
+    # bits, g, M, N, K -- one case per kernel: decode (clusters, whole row blocks, stream-K),
+    # cluster split-K streaming kernel, general kernel, tensor-core GEMM (plain and split-K)
+    (4, 128, 4, 1024, 4096), (4, 128, 16, 14336, 1024), (4, 128, 3, 20000, 1024), (4, 16, 5, 320, 512),
+    (4, 24, 7, 64, 96), (4, 128, 64, 1024, 2048), (4, 128, 300, 512, 1024), (2, 64, 4096, 256, 512),
+], ids=lambda c: "b%d_g%d_M%d_N%d_K%d" % c)
+def test_fused_relu_and_residual_equal_the_separate_ops(case):
+    # bw_qmatmul_fused: relu(linear) + residual inside the kernel's output stage must give the
+    # bits of the unfused sequence (fp16 op by op) for fp16 outputs
+    bits, g, M, N, K = case
+    q, s_h, z_h, b_h = _make_layer(hash(case) % 100000, N, K, bits, g, True)
+    x = torch.from_numpy(synth.normal(5 + M, (M, K), 1.0)).half().to(DEV)
+    res = torch.from_numpy(synth.normal(6 + M, (M, N), 1.0)).half().to(DEV)
+    dev = [t.to(DEV) for t in (q, s_h, z_h, b_h)]
+    plain = quantized_matmul_cuda(x, *dev, bits, g)
+    kern = _lib.last_qmatmul_kernel()
+    fused = quantized_matmul_cuda(x, *dev, bits, g, activation="relu", residual=res)
+    assert _lib.last_qmatmul_kernel() == kern
+    assert torch.equal(fused, torch.relu(plain) + res), (case, kern)
+    only_relu = quantized_matmul_cuda(x, *dev, bits, g, activation="relu")
+    assert torch.equal(only_relu, torch.relu(plain))
+    # in place on the residual buffer (the usual `h = h + mlp(h)`)
+    buf = res.clone()
+    quantized_matmul_cuda(x, *dev, bits, g, residual=buf, out=buf)
+    assert torch.equal(buf, plain + res)
+    # fp32 output: one rounding at the end
+    f32 = quantized_matmul_cuda(x, *dev, bits, g, out_dtype=torch.float32, activation="relu", residual=res)
+    ref = torch.relu(quantized_matmul_cuda(x, *dev, bits, g, out_dtype=torch.float32)) + res.float()
+    assert torch.allclose(f32, ref, rtol=0, atol=1e-6 * float(ref.abs().max()))
+    assert _lib.lib().bw_device_status() == 0
