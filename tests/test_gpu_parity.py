@@ -552,3 +552,32 @@ def test_fused_relu_and_residual_equal_the_separate_ops(case):
     ref = torch.relu(quantized_matmul_cuda(x, *dev, bits, g, out_dtype=torch.float32)) + res.float()
     assert torch.allclose(f32, ref, rtol=0, atol=1e-6 * float(ref.abs().max()))
     assert _lib.lib().bw_device_status() == 0
+
+
+@pytest.mark.parametrize("bits,g,gdt,shape", [
+    (4, 128, torch.float16, (300, 200, 384)), (4, 64, torch.bfloat16, (129, 48, 192)),
+    (8, 32, torch.float16, (16, 130, 96)), (2, 64, torch.bfloat16, (257, 64, 1024)), (4, 24, torch.float16, (33, 18, 96)),
+], ids=lambda v: str(v).replace(" ", ""))
+def test_grad_input_tensor_core_kernel_vs_oracle(bits, g, gdt, shape):
+    # 16-bit gradients run on mma.sync tiles of 128 tokens x 64 k over steps of 16 weight rows:
+    # ragged M, N and K tails, every bit width, groups that split a packed word (g = 24)
+    M, N, K = shape
+    q, s_h, z_h, _ = _make_layer(950 + bits + M, N, K, bits, g, False)
+    go = torch.from_numpy(synth.normal(951, (M, N), 1.0)).to(gdt)
+    ref = from_bits(oracle.qlinear_grad_input(to_np(go), ORACLE_DT[gdt], to_np(q), to_np(s_h), to_np(z_h), bits, g), gdt)
+    gi = quantized_matmul_grad_input(go.to(DEV), q.to(DEV), s_h.to(DEV), z_h.to(DEV), bits, g)
+    assert gi.dtype == gdt and tuple(gi.shape) == (M, K)
+    if gdt == torch.bfloat16:
+        # one bf16 ulp of the value on top of the bar: the final rounding alone moves a value by
+        # up to 2^-8 |y|, more than 1e-2 * RMS for |y| > 2.6 RMS, whenever the fp32 sums differ
+        # in their last bits (other summation order)
+        err = np.abs(as_f32(gi) - as_f32(ref))
+        assert (err <= 1e-2 * rms(as_f32(ref)) + 2.0 ** -8 * np.abs(as_f32(ref))).all(), shape
+    else:
+        assert_close_rms(as_f32(gi), as_f32(ref), 1e-2, str(shape))
+    # and the same numbers as the CUDA-core kernel gives on fp32 copies of the same operands
+    # (W is rounded to the gradient dtype in both, products are exact, sums are fp32)
+    w = dequantize_rtn(q.to(DEV), s_h.to(DEV), z_h.to(DEV), g, bits=bits).to(gdt).float()
+    full = go.to(DEV).float() @ w
+    slack = 2.0 ** -8 * full.abs() if gdt == torch.bfloat16 else 0.0
+    assert bool(((gi.float() - full).abs() <= 1e-2 * rms(as_f32(full)) + slack).all())
