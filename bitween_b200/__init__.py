@@ -5,7 +5,7 @@ library as hand-written sm_100a CUDA behind a C ABI, with the reference's Python
 
 `install_as_bitween()` registers the package under the name `bitween` so that code and pickles
 written against the reference (`bitween.modules.QuantizedLinear`, `bitween.functional`,
-`bitween.kernels.cuda_loader`, `bitween.gradual.base_wrapper.RTNWrapper`) resolve to this implementation.
+`bitween.kernels.cuda_loader`, `bitween.gradual.base_wrapper.RTNWrapper`, `bitween.wrapper.WrapperLinear`) resolve to this implementation.
 """
 import sys
 
@@ -18,7 +18,7 @@ __version__ = "0.1.0"
 
 def install_as_bitween():
     """Alias this package as `bitween` in sys.modules (drop-in for imports and unpickling)."""
-    from . import functional, gradual, kernels, modules, quantizer
+    from . import functional, gradual, kernels, modules, quantizer, wrapper
     from .gradual import base_wrapper
     from .kernels import cuda_loader
     from .quantizer import func as qfunc, quantizer as qq
@@ -30,6 +30,7 @@ def install_as_bitween():
     sys.modules["bitween.kernels.cuda_loader"] = cuda_loader
     sys.modules["bitween.gradual"] = gradual
     sys.modules["bitween.gradual.base_wrapper"] = base_wrapper
+    sys.modules["bitween.wrapper"] = wrapper
     sys.modules["bitween.quantizer"] = quantizer
     sys.modules["bitween.quantizer.quantizer"] = qq
     sys.modules["bitween.quantizer.func"] = qfunc

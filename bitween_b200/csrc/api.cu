@@ -53,6 +53,10 @@ void set_decode_tuning(int enabled, int smem_kb, int max_ctas, int pdl);
 int qmatmul_decode(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
                    const __half *scale, const __half *zp, const __half *bias, void *out, int out_dtype,
                    int bits, int g, void *workspace, cudaStream_t st);
+int fake_quant(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int g, const float *scale, const float *zp,
+               const void *value, int value_dtype, float *dq, float *wq, cudaStream_t st);
+int fake_quant_backward(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int g, const float *scale, const float *zp,
+                        const void *value, int value_dtype, const float *grad, float *gscale, float *gzp, cudaStream_t st);
 int rtn_device_status();
 long long div_self_check(unsigned long long n, unsigned long long seed);
 int qmatmul_grad_input(const void *go, int dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
@@ -319,6 +323,38 @@ int bw_qmatmul_grad_input(const void *grad_out, int grad_dtype, int64_t M, int64
     return qmatmul_grad_input(grad_out, grad_dtype, M, N, K, qweight, (const __half *)scale,
                               (const __half *)zero_point, grad_in, bits, group_size,
                               (cudaStream_t)stream);
+}
+
+int bw_fake_quant(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int group_size, const float *scale,
+                  const float *zero_point, const void *value, int value_dtype, float *w_dq, float *w_q, void *stream) {
+    if (bits != 2 && bits != 4 && bits != 8) return BW_ERR_BITS;
+    if (group_size < 1) return BW_ERR_GROUP;
+    if (N < 0 || K < 0) return BW_ERR_SHAPE;
+    if (K % group_size != 0) return BW_ERR_GROUP;
+    if (!is_float_dtype(w_dtype) || (value && !is_float_dtype(value_dtype))) return BW_ERR_DTYPE;
+    if (N * K == 0) return BW_OK;
+    if (!w || !scale || !zero_point || !w_dq) return BW_ERR_NULL;
+    if (!aligned_to(w, dtype_size(w_dtype)) || !aligned_to(scale, 4) || !aligned_to(zero_point, 4) ||
+        (value && !aligned_to(value, dtype_size(value_dtype))) ||
+        !aligned_to(w_dq, 4) || !aligned_to(w_q, 4))
+        return BW_ERR_ALIGN;
+    return fake_quant(w, w_dtype, N, K, bits, group_size, scale, zero_point, value, value_dtype, w_dq, w_q, (cudaStream_t)stream);
+}
+
+int bw_fake_quant_backward(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int group_size, const float *scale,
+                           const float *zero_point, const void *value, int value_dtype, const float *grad_w_dq,
+                           float *grad_scale, float *grad_zero_point, void *stream) {
+    if (bits != 2 && bits != 4 && bits != 8) return BW_ERR_BITS;
+    if (group_size < 1) return BW_ERR_GROUP;
+    if (N < 0 || K < 0) return BW_ERR_SHAPE;
+    if (K % group_size != 0) return BW_ERR_GROUP;
+    if (!is_float_dtype(w_dtype) || (value && !is_float_dtype(value_dtype))) return BW_ERR_DTYPE;
+    if (N * K == 0) return BW_OK;
+    if (!w || !scale || !zero_point || !grad_w_dq || !grad_scale || !grad_zero_point) return BW_ERR_NULL;
+    if (!aligned_to(scale, 4) || !aligned_to(zero_point, 4) || !aligned_to(grad_scale, 4) || !aligned_to(grad_zero_point, 4))
+        return BW_ERR_ALIGN;
+    return fake_quant_backward(w, w_dtype, N, K, bits, group_size, scale, zero_point, value, value_dtype, grad_w_dq, grad_scale,
+                               grad_zero_point, (cudaStream_t)stream);
 }
 
 const char *bw_status_string(int status) {

@@ -60,6 +60,10 @@ def _declare(L):
     L.bw_rtn_batch_table_bytes.restype = sz
     L.bw_rtn_quantize_pack_batch.argtypes = [ctypes.POINTER(RtnJob), i32, i32, i32, i32, i32, i32, u32, vp, sz, vp]
     L.bw_rtn_quantize_pack_batch.restype = i32
+    L.bw_fake_quant.argtypes = [vp, i32, i64, i64, i32, i32, vp, vp, vp, i32, vp, vp, vp]
+    L.bw_fake_quant.restype = i32
+    L.bw_fake_quant_backward.argtypes = [vp, i32, i64, i64, i32, i32, vp, vp, vp, i32, vp, vp, vp, vp]
+    L.bw_fake_quant_backward.restype = i32
     L.bw_dequantize.argtypes = [vp, vp, i32, vp, i32, i64, i64, i32, i32, vp, i32, vp]
     L.bw_dequantize.restype = i32
     L.bw_qmatmul_workspace_bytes.argtypes = [i64, i64, i64, i32, i32]

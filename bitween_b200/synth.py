@@ -39,3 +39,9 @@ def normal(seed, shape, std=1.0, terms=8):
 def randint(seed, shape, high):
     n = int(np.prod(shape))
     return (uniform01(seed, n, stream=99) * high).astype(np.int64).reshape(shape)
+
+
+def uniform(seed, shape, lo=0.0, hi=1.0):
+    """float32 array uniform in [lo, hi)."""
+    n = int(np.prod(shape))
+    return (lo + (hi - lo) * uniform01(seed, n, stream=77)).astype(np.float32).reshape(shape)

@@ -251,6 +251,40 @@ BW_API int bw_qmatmul_grad_input(const void *grad_out, int grad_dtype, int64_t M
                           const int32_t *qweight, const void *scale, const void *zero_point,
                           void *grad_in, int bits, int group_size, void *stream);
 
+/*
+ * Fake-quantized weights of the trainable mode: the elementwise part of
+ * WrapperLinear._quantize_weight_with_learnable_params (bitween/wrapper.py:143-155), evaluated
+ * on every training step there, as one pass.  The per-group scale and FLOAT zero point are
+ * inputs (the caller derives them from the group minima / maxima and the learnable factors,
+ * bitween/wrapper.py:127-140, on [N, K/group_size] tensors, where autograd tracks them):
+ *     t    = w / scale + zero_point (+ value)
+ *     w_q  = clamp(round_half_even(t), 0, 2^bits - 1)
+ *     w_dq = scale * (w_q - zero_point)
+ * in fp32, one rounding per operation in this order: bit-identical to the reference in fp32.
+ *   w [N,K] BW_F32 | BW_F16 | BW_BF16 (up-cast exactly)   scale, zero_point [N,K/group_size] fp32
+ *   value [N,K] of value_dtype (BW_F32 | BW_F16 | BW_BF16) or NULL
+ *   w_dq [N,K] fp32 out           w_q [N,K] fp32 out or NULL
+ */
+BW_API int bw_fake_quant(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int group_size,
+                  const float *scale, const float *zero_point, const void *value, int value_dtype,
+                  float *w_dq, float *w_q, void *stream);
+
+/*
+ * Backward of bw_fake_quant for the per-group parameters, as the reference's autograd graph
+ * gives it (round() passes no gradient, bitween/wrapper.py:152-155):
+ *     grad_scale      = sum over the group of grad_w_dq * (w_q - zero_point)
+ *     grad_zero_point = -scale * sum over the group of grad_w_dq
+ * w_q is recomputed from w (and value); `value` itself receives no gradient.  Sums are fp32 in
+ * a fixed order (deterministic), not the order of torch's reduction: compare to ~1e-5 relative.
+ * group_size must be 4 * 2^j <= 128 and w, value, grad_w_dq aligned to four elements,
+ * else BW_ERR_GROUP / BW_ERR_ALIGN (the caller then uses its own reduction).
+ *   grad_w_dq [N,K] fp32      grad_scale, grad_zero_point [N,K/group_size] fp32 out
+ */
+BW_API int bw_fake_quant_backward(const void *w, int w_dtype, int64_t N, int64_t K, int bits,
+                           int group_size, const float *scale, const float *zero_point,
+                           const void *value, int value_dtype, const float *grad_w_dq,
+                           float *grad_scale, float *grad_zero_point, void *stream);
+
 /* Human-readable text for a bw_status. */
 BW_API const char *bw_status_string(int status);
 /* Text of the last CUDA error seen by this thread inside the library ("" if none). */

@@ -184,3 +184,47 @@ def qlinear_grad_input(grad_out, grad_dtype, q, scale_h, zp_h, bits, group_size)
                                       _p(zp_h), bits, group_size, _p(out))
     _check(rc, "qlinear_grad_input")
     return out
+
+
+def wrapper_group_params(w32, bits, group_size, min_scale=None, max_scale=None):
+    """scale, zero_point [N,G] fp32 of bitween/wrapper.py:127-140 for weights already up-cast to
+    fp32 (exact for 16-bit weights; the products below are fp32 there because the factors are)."""
+    w32 = np.asarray(w32, dtype=np.float32)
+    N, K = w32.shape
+    grouped = w32.reshape(N, K // group_size, group_size)
+    w_min, w_max = grouped.min(-1), grouped.max(-1)
+    if min_scale is not None and max_scale is not None:
+        w_min = w_min * np.asarray(min_scale, dtype=np.float32)
+        w_max = w_max * np.asarray(max_scale, dtype=np.float32)
+    with np.errstate(all="ignore"):
+        scale = (w_max - w_min) / np.float32((1 << bits) - 1)
+        scale = np.where(scale < np.float32(1e-8), np.float32(1e-8), scale).astype(np.float32)   # clamp(min=): NaN stays
+        zp = (-w_min / scale).astype(np.float32)
+    return scale, zp
+
+
+def wrapper_fake_quant(w32, scale, zp, value32, bits, group_size):
+    """w_dq, w_q [N,K] fp32 of bitween/wrapper.py:143-155: one fp32 rounding per operation."""
+    w32 = np.asarray(w32, dtype=np.float32)
+    N, K = w32.shape
+    s3 = np.asarray(scale, dtype=np.float32)[:, :, None]
+    z3 = np.asarray(zp, dtype=np.float32)[:, :, None]
+    with np.errstate(all="ignore"):
+        t = w32.reshape(N, K // group_size, group_size) / s3 + z3
+        if value32 is not None:
+            t = t + np.asarray(value32, dtype=np.float32).reshape(t.shape)
+        r = np.rint(t)
+        q = np.where(np.isnan(r), r, np.minimum(np.maximum(r, np.float32(0)), np.float32((1 << bits) - 1))).astype(np.float32)
+        dq = (s3 * (q - z3)).astype(np.float32)
+    return dq.reshape(N, K), q.reshape(N, K)
+
+
+def wrapper_param_grads(w32, scale, zp, value32, grad, bits, group_size):
+    """d/d scale and d/d zero_point of sum(w_dq * grad) as the reference's autograd graph gives
+    them (round has zero gradient), accumulated in float64."""
+    _, q = wrapper_fake_quant(w32, scale, zp, value32, bits, group_size)
+    N, K = q.shape
+    g3 = np.asarray(grad, dtype=np.float64).reshape(N, K // group_size, group_size)
+    q3 = q.astype(np.float64).reshape(g3.shape)
+    z = np.asarray(zp, dtype=np.float64)
+    return (g3 * (q3 - z[:, :, None])).sum(-1), -np.asarray(scale, dtype=np.float64) * g3.sum(-1)

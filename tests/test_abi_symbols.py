@@ -47,3 +47,15 @@ def test_status_strings_and_argument_validation_need_no_gpu():
     # more tokens: the fp16 cast of the activations for the tensor-core GEMM
     assert L.bw_qmatmul_workspace_bytes(64, 4096, 4096, 4, 128) == 64 * 4096 * 2
     assert L.bw_qmatmul_workspace_bytes(0, 8, 64, 4, 32) == 0
+    # the query that knows the activation dtype: aligned fp16 activations go to the tensor cores as they
+    # are, so only the 64-token scratch of the streaming kernel (its stand-in for odd layouts) is asked for
+    assert L.bw_qmatmul_workspace_bytes_for(4096, 4096, 4096, 4, 128, 1, 16) == 64 * 4096 * 2
+    assert L.bw_qmatmul_workspace_bytes_for(4096, 4096, 4096, 4, 128, 2, 16) == 4096 * 4096 * 2
+    assert L.bw_qmatmul_workspace_bytes_for(4096, 4096, 4096, 4, 128, 1, 2) == 4096 * 4096 * 2
+    # fake quantization of the trainable mode: argument rules before any CUDA call
+    assert L.bw_fake_quant(z, 0, 4, 64, 3, 32, z, z, z, 0, z, z, z) == 1
+    assert L.bw_fake_quant(z, 0, 4, 48, 4, 32, z, z, z, 0, z, z, z) == 2
+    assert L.bw_fake_quant(z, 9, 4, 64, 4, 32, z, z, z, 0, z, z, z) == 4
+    assert L.bw_fake_quant(z, 0, 4, 64, 4, 32, z, z, z, 0, z, z, z) == 6
+    assert L.bw_fake_quant(z, 0, 0, 64, 4, 32, z, z, z, 0, z, z, z) == 0
+    assert L.bw_fake_quant_backward(z, 0, 4, 64, 4, 32, z, z, z, 0, z, z, z, z) == 6

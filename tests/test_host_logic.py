@@ -178,3 +178,55 @@ def test_rtn_wrapper_quantizes_a_block_once_per_config_and_restores_it(monkeypat
     small = RTNCache(max_bytes=1)
     quantize_block(block, 8, 32, small)
     assert len(small) == 1
+
+
+def test_wrapper_linear_host_logic_with_oracle_doubles(monkeypatch):
+    """WrapperLinear's bookkeeping (buffers, parameters, wrap / unwrap, best-parameter tracking)
+    with the two CUDA calls replaced by the oracle: no GPU needed."""
+    import numpy as np
+    from bitween_b200 import wrapper
+
+    def rtn_double(weight, bits=8, group_size=32):
+        q, s, z = oracle.quantize_rtn(to_np(weight.float()), oracle.F32, bits, group_size)
+        return torch.from_numpy(q), torch.from_numpy(s), torch.from_numpy(z), weight.shape
+
+    def fq_double(weight, scale, zero_point, value, bits, group_size, want_q=True):
+        dq, q = oracle.wrapper_fake_quant(weight.detach().float().numpy(), scale.detach().numpy(),
+                                          zero_point.detach().numpy(),
+                                          None if value is None else value.detach().float().numpy(), bits, group_size)
+        return torch.from_numpy(dq), torch.from_numpy(q)
+
+    monkeypatch.setattr(wrapper, "quantize_rtn", rtn_double)
+    monkeypatch.setattr(wrapper, "fake_quantize", fq_double)
+    torch.manual_seed(0)
+    block = nn.Sequential(nn.Linear(64, 32), nn.ReLU(), nn.Linear(32, 64, bias=False))
+    buf = io.StringIO()
+    with redirect_stdout(buf):
+        _, names = wrapper.unified_wrapper(block, bits=4, group_size=32, ignore_layers={"blk.2"}, module_prefix="blk")
+    assert names == ["0"] and "Skipping ignored layer: blk.2" in buf.getvalue()
+    wl = block[0]
+    assert isinstance(wl, wrapper.WrapperLinear) and isinstance(block[2], nn.Linear)
+    assert list(wl.state_dict()) == ["value", "min_scale", "max_scale", "orig_weight", "orig_bias", "base_qweight",
+                                     "base_scale", "base_zero_point", "orig_layer.weight", "orig_layer.bias"]
+    assert tuple(wl.min_scale.shape) == (32, 2) and wl.value.shape == wl.orig_weight.shape
+    w_dq, w_q, scale, zp = wl._quantize_weight_with_learnable_params()
+    assert tuple(w_q.shape) == (32, 2, 32) and tuple(scale.shape) == (32, 2)
+    # untouched parameters: fake quantization is plain RTN with a float zero point
+    assert float((w_dq - wl.orig_weight).abs().max()) <= float(scale.detach().max()) * 0.5 + 1e-7
+    assert block(torch.randn(3, 64)).shape == (3, 64)
+    off = wrapper.WrapperLinear(nn.Linear(64, 8), bits=2, group_size=64, enable_minmax_tuning=False,
+                                enable_round_tuning=False)
+    assert off.value is None and off.min_scale is None and off.max_scale is None
+    assert list(off.state_dict())[:2] == ["orig_weight", "orig_bias"]
+    wl.update_best_params(3.0)
+    with torch.no_grad():
+        wl.value.add_(0.25)
+    wl.update_best_params(5.0)
+    assert wl.best_loss == 3.0 and float(wl.best_params["value"].abs().max()) == 0.0
+    q, un = wrapper.wrapper_block(nn.Sequential(nn.Linear(32, 32)), bits=8, group_size=32)
+    assert q == ["0"] and "" in un
+    ql = wrapper.unified_unwrapper(wl, apply_quantization=True)
+    assert isinstance(ql, QuantizedLinear) and float(wl.value.abs().max()) == 0.0    # best parameters applied
+    want_q, want_s, want_z = oracle.quantize_rtn(to_np(wl.orig_weight), oracle.F32, 4, 32)
+    assert np.array_equal(to_np(ql.qweight), want_q)
+    assert wrapper.unified_unwrapper(wl, apply_quantization=False) is wl.orig_layer
