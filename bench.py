@@ -52,10 +52,18 @@ LLAMA70B_LINEARS = [("q_proj", HIDDEN70, HIDDEN70, "column"), ("k_proj", KV70, H
                     ("gate_proj", FFN70, HIDDEN70, "column"), ("up_proj", FFN70, HIDDEN70, "column"),
                     ("down_proj", HIDDEN70, FFN70, "row")]
 
-# DRAM bytes of one qmm_decode_kernel launch divided by its algorithmic bytes, from ncu captures
-# of single launches (dram__bytes_read.sum + dram__bytes_write.sum) at 1 and 16 tokens; constants
-# from those profiles, not measured during the run.
-DECODE_TRAFFIC_FACTOR = {"q_o_proj": 1.004, "kv_proj": 1.02, "gate_up_proj": 1.001, "down_proj": 1.001}
+# DRAM bytes of one qmm_decode_kernel launch (dram__bytes_read.sum + dram__bytes_write.sum of an ncu
+# capture of `bench.py --case decode:<shape>:<tokens>`, second captured launch) divided by its
+# algorithmic bytes, at 1 and 16 tokens per shape; token counts in between are interpolated.
+# Constants from those captures, not measured during the run.  Below 1.0: the outputs (and part of
+# the activations) never leave L2 within the launch.
+DECODE_TRAFFIC_FACTOR = {"q_o_proj": {1: 1.0064, 16: 0.9937}, "kv_proj": {1: 1.0285, 16: 1.0170},
+                         "gate_up_proj": {1: 1.0012, 16: 0.9881}, "down_proj": {1: 1.0019, 16: 0.9982}}
+
+
+def decode_traffic_factor(name, M):
+    f1, f16 = DECODE_TRAFFIC_FACTOR[name][1], DECODE_TRAFFIC_FACTOR[name][16]
+    return f1 + (f16 - f1) * (min(max(M, 1), 16) - 1) / 15.0
 
 
 def decode_bytes(M, N, K, bits, g, bias=False):
@@ -270,7 +278,8 @@ def run_decode8b(args, torch, dist, rank, world, device):
     launches_per_step = calls_per_step                      # the decode kernel is the only launch of a call
     per_shape = {name: sum(decode_bytes(M, N, K, bits, g) for M in DECODE_M) for (name, N, K) in LLAMA8B_SHAPES}
     bytes_per_step = sum(per_shape.values()) * args.layers
-    traffic_per_step = sum(per_shape[n] * DECODE_TRAFFIC_FACTOR[n] for n in per_shape) * args.layers
+    traffic_per_step = sum(decode_bytes(M, N, K, bits, g) * decode_traffic_factor(name, M)
+                           for M in DECODE_M for (name, N, K) in LLAMA8B_SHAPES) * args.layers
 
     for _ in range(max(args.warmup, 1) if not args.graph else 1):
         step()
@@ -311,7 +320,24 @@ def run_decode8b(args, torch, dist, rank, world, device):
         e2e_step()
     e2e_steps = max(1, min(args.steps, 5))
     ms_e2e = max_over_ranks(torch, dist, device, time_region(torch, lambda: [e2e_step() for _ in range(e2e_steps)]))
-    e2e_val = bytes_per_step * e2e_steps * world / (ms_e2e * 1e-3) / 1e9
+    e2e_eager = bytes_per_step * e2e_steps * world / (ms_e2e * 1e-3) / 1e9
+    e2e_val, e2e_mode = e2e_eager, "eager: one host-buffer call per linear, issued from Python"
+    if args.graph:
+        # the same calls captured once as a CUDA graph (per call, in stream order: the staging of the
+        # pinned activations to the device, the kernel, the staging of the outputs to pinned host
+        # memory) and replayed per step, the way a serving loop issues a fixed step; the caller
+        # refills the pinned input buffers between replays
+        torch.cuda.synchronize()
+        e2e_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(e2e_graph):
+            e2e_step()
+        for _ in range(2):
+            e2e_graph.replay()
+        ms_g = max_over_ranks(torch, dist, device,
+                              time_region(torch, lambda: [e2e_graph.replay() for _ in range(e2e_steps)]))
+        e2e_val = bytes_per_step * e2e_steps * world / (ms_g * 1e-3) / 1e9
+        e2e_mode = ("cuda graph of the host-buffer calls (per call: pinned host -> device staging of the activations, "
+                    "kernel, device -> pinned host staging of the outputs), replayed per step")
 
     # ---- per-shape breakdown (M = 1 and 16): the layer copies of one shape replayed as one graph,
     # L2 flushed before every replay ----
@@ -340,12 +366,13 @@ def run_decode8b(args, torch, dist, rank, world, device):
     return {"value": value, "ms": ms, "launches": launches_per_step * args.steps, "calls": calls_per_step * args.steps,
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps},
+                    "steps": e2e_steps, "mode": e2e_mode, "eager_value": e2e_eager},
             "bytes_per_launch": bytes_per_step / calls_per_step, "launches_per_step": launches_per_step,
             "breakdown": breakdown, "kernel": decode_kernel,
             "traffic": traffic_per_step / calls_per_step,
-            "traffic_source": "constant from ncu profiles of single launches (DRAM bytes / algorithmic bytes per shape: "
-                              + ", ".join(f"{k} {v}" for k, v in DECODE_TRAFFIC_FACTOR.items()) + "), weighted over the sweep",
+            "traffic_source": "constants from ncu captures of single launches (DRAM bytes / algorithmic bytes per shape at "
+                              "1 and 16 tokens: " + ", ".join(f"{k} {v[1]}/{v[16]}" for k, v in DECODE_TRAFFIC_FACTOR.items())
+                              + "), interpolated in the token count and weighted over the sweep",
             "config": config}
 
 
@@ -403,7 +430,92 @@ def run_single_gpu_extras(args, torch, device, gen):
                 del x, y
             del L
         out[f"prefill_w{bits}g{g}_TFLOPs"] = pf
+    # backward of the frozen layer (grad_input = grad_output @ W, bitween/modules.py:108-141) at 4096 tokens
+    from bitween_b200.kernels.cuda_loader import quantized_matmul_grad_input as qgrad
+    gi = {}
+    for (name, N, K) in LLAMA8B_SHAPES:
+        L = Layer(N, K, 4, 128, device, gen, torch, fn)
+        go = torch.randn(4096, N, device=device, generator=gen).to(torch.float16)
+        ms = graph_ms(torch, lambda: [qgrad(go, L.q, L.scale, L.zp, 4, 128) for _ in range(3)], flush, reps=3) / 3
+        gi[f"{name}_{N}x{K}_M4096"] = round(2.0 * 4096 * N * K / (ms * 1e-3) / 1e12, 1)
+        del L, go
+    out["grad_input_w4g128_TFLOPs"] = gi
+    # trainable mode: fake-quantized weight of WrapperLinear (bitween/wrapper.py:116-172), forward and the
+    # backward for the per-group factors, bf16 weights W4 g128; bytes = weight + perturbation in, fp32 out
+    from bitween_b200.wrapper import WrapperLinear
+    fq = {}
+    for (name, N, K) in LLAMA8B_SHAPES[2:3]:
+        lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16, device=device)
+        wl = WrapperLinear(lin, bits=4, group_size=128)
+        r = torch.randn(N, K, device=device, generator=gen)
+
+        def fwd_bwd():
+            wl.min_scale.grad = wl.max_scale.grad = None
+            w_dq = wl._quantize_weight_with_learnable_params()[0]
+            w_dq.backward(r)
+        with torch.no_grad():
+            ms_f = graph_ms(torch, lambda: wl._quantize_weight_with_learnable_params(), flush, reps=3)
+        fwd_bwd()
+        torch.cuda.synchronize()
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(5):
+            fwd_bwd()
+        t1.record()
+        torch.cuda.synchronize()
+        fq[f"{name}_{N}x{K}_forward_GBps"] = round(N * K * (2 + 2 + 4 + 4) / (ms_f * 1e-3) / 1e9, 1)
+        fq[f"{name}_{N}x{K}_forward_backward_us"] = round(t0.elapsed_time(t1) / 5 * 1e3, 1)
+        del wl, lin, r
+    out["fake_quant_w4g128_bf16"] = fq
     return out
+
+
+def run_case(args, torch, device):
+    """`--case kind:shape:tokens[:bits[:group]]` -- one kernel on one Llama-3-8B shape, a handful of
+    plain (ungraphed) launches over 4 distinct layer copies, so that a profiler can capture a single
+    launch without the rest of the benchmark.  kind: decode | prefill (both the qmatmul call),
+    rtn, gradinput, fakequant.  Prints one small JSON line with the CUDA-event time per launch."""
+    from bitween_b200 import functional as fn
+    from bitween_b200.kernels import _lib
+    from bitween_b200.kernels.cuda_loader import quantized_matmul_cuda as qmm, quantized_matmul_grad_input as qgrad
+    parts = args.case.split(":")
+    kind, shape = parts[0], parts[1]
+    M = int(parts[2]) if len(parts) > 2 else 1
+    bits = int(parts[3]) if len(parts) > 3 else 4
+    g = int(parts[4]) if len(parts) > 4 else 128
+    name, N, K = next(t for t in LLAMA8B_SHAPES if t[0] == shape)
+    gen = torch.Generator(device=device).manual_seed(5)
+    copies = 4
+    if kind in ("decode", "prefill", "gradinput"):
+        layers = [Layer(N, K, bits, g, device, gen, torch, fn) for _ in range(copies)]
+        if kind == "gradinput":
+            a = torch.randn(M, N, device=device, generator=gen).to(torch.float16)
+            body = lambda L: qgrad(a, L.q, L.scale, L.zp, bits, g)
+        else:
+            x = torch.randn(M, K, device=device, generator=gen).to(torch.bfloat16)
+            y = torch.empty(M, N, device=device, dtype=torch.float16)
+            body = lambda L: qmm(x, L.q, L.scale, L.zp, None, bits, g, out=y)
+    elif kind == "rtn":
+        layers = [(torch.randn(N, K, device=device, generator=gen) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+        body = lambda w: fn._rtn_launch(w, bits, g, torch.float32, torch.int32, True)
+    elif kind == "fakequant":
+        from bitween_b200.wrapper import WrapperLinear, fake_quantize
+        layers = [WrapperLinear(torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16, device=device), bits=bits, group_size=g)
+                  for _ in range(copies)]
+        r = torch.randn(N, K, device=device, generator=gen)
+
+        def body(wl):
+            wl.min_scale.grad = wl.max_scale.grad = None
+            wl._quantize_weight_with_learnable_params()[0].backward(r)
+    else:
+        raise SystemExit(f"unknown case kind {kind!r}")
+    for L in layers:                       # warm-up pass (also the launches a profiler skips)
+        body(L)
+    ms = time_region(torch, lambda: [body(L) for L in layers]) / copies
+    print(json.dumps({"case": args.case, "kernel": _lib.last_qmatmul_kernel() if kind in ("decode", "prefill") else kind,
+                      "us_per_launch": round(ms * 1e3, 2), "copies": copies,
+                      "note": "plain launches, back to back, no L2 flush: a profiling aid, not a benchmark value"}), flush=True)
 
 
 def shard_shape(N, K, mode, world):
@@ -555,6 +667,7 @@ def main():
     ap.add_argument("--graph", type=int, default=1, help="replay each step as one CUDA graph")
     ap.add_argument("--tp-layers", type=int, default=3, help="70B-shaped decoder layers of the tensor-parallel workload")
     ap.add_argument("--rtn-layers", type=int, default=80, help="70B-shaped layers whose weights the sharded RTN run quantizes")
+    ap.add_argument("--case", default="", help="kind:shape:tokens[:bits[:group]] -- run one kernel on one shape (for profilers)")
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -578,6 +691,12 @@ def main():
         import torch.distributed as dist_mod
         dist_mod.init_process_group("nccl", device_id=device)
         dist = dist_mod
+
+    if args.case:
+        if world > 1:
+            raise SystemExit("--case runs on one GPU")
+        run_case(args, torch, device)
+        return
 
     res = run_decode8b(args, torch, dist, rank, world, device)
     extra = {}

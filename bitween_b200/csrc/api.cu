@@ -286,6 +286,61 @@ size_t bw_qmatmul_noalloc_max_scratch_bytes(void) {
     return noalloc_scratch(&p, &b) == BW_OK ? b : 0;
 }
 
+// Staging between pinned host memory and the device for bw_qmatmul_host.  Decode-sized
+// activations and outputs are a few KB to a few hundred KB: a copy engine needs several
+// microseconds of set-up per transfer and serialises with the kernel, so they are moved by a
+// small kernel instead -- plain 16-byte loads / stores on the host buffer's device mapping
+// (pinned memory is mapped into the unified address space), launched with programmatic
+// stream serialisation so that its launch latency overlaps its predecessor.
+__global__ void __launch_bounds__(256) staging_copy_kernel(const unsigned char *__restrict__ src,
+                                                           unsigned char *__restrict__ dst, size_t bytes) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");      // dst may still be read, src still be written, by the predecessor
+    const size_t n16 = bytes / 16;
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = tid; i < n16; i += stride)
+        reinterpret_cast<uint4 *>(dst)[i] = reinterpret_cast<const uint4 *>(src)[i];
+    for (size_t i = n16 * 16 + tid; i < bytes; i += stride) dst[i] = src[i];
+}
+
+// The device-side address of a pinned (mapped) host buffer, or nullptr.
+static void *device_view_of_host(const void *host) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, host) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    return a.type == cudaMemoryTypeHost ? a.devicePointer : nullptr;
+}
+
+static constexpr size_t STAGING_KERNEL_MAX_BYTES = (size_t)4 << 20;   // larger transfers go to the copy engines
+
+static int staging_copy(void *dst, const void *src, size_t bytes, cudaMemcpyKind kind, cudaStream_t st) {
+    if (bytes == 0) return BW_OK;
+    const void *host = kind == cudaMemcpyHostToDevice ? src : dst;
+    void *mapped = bytes <= STAGING_KERNEL_MAX_BYTES && aligned_to(dst, 16) && aligned_to(src, 16) ? device_view_of_host(host) : nullptr;
+    if (!mapped) {
+        BW_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, kind, st));
+        return BW_OK;
+    }
+    const void *s = kind == cudaMemcpyHostToDevice ? mapped : src;
+    void *d = kind == cudaMemcpyHostToDevice ? dst : mapped;
+    size_t blocks = (bytes / 16 + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 64) blocks = 64;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BW_CUDA_TRY(cudaLaunchKernelEx(&cfg, staging_copy_kernel, (const unsigned char *)s, (unsigned char *)d, bytes));
+    return BW_OK;
+}
+
 int bw_qmatmul_host(const void *x_host, int x_dtype, int64_t M, int64_t N, int64_t K,
                     const int32_t *qweight, const void *scale, const void *zero_point,
                     const void *bias, void *out_host, int out_dtype, int bits, int group_size,
@@ -296,15 +351,12 @@ int bw_qmatmul_host(const void *x_host, int x_dtype, int64_t M, int64_t N, int64
     if (M * N == 0) return BW_OK;
     if (!x_dev || !out_dev || !out_host || (K > 0 && !x_host)) return BW_ERR_NULL;
     cudaStream_t st = (cudaStream_t)stream;
-    if (M * K > 0)
-        BW_CUDA_TRY(cudaMemcpyAsync(x_dev, x_host, (size_t)(M * K) * dtype_size(x_dtype),
-                                    cudaMemcpyHostToDevice, st));
-    int rc = bw_qmatmul(x_dev, x_dtype, M, N, K, qweight, scale, zero_point, bias, out_dev, out_dtype,
-                        bits, group_size, workspace, workspace_bytes, stream);
+    int rc = staging_copy(x_dev, x_host, (size_t)(M * K) * dtype_size(x_dtype), cudaMemcpyHostToDevice, st);
     if (rc != BW_OK) return rc;
-    BW_CUDA_TRY(cudaMemcpyAsync(out_host, out_dev, (size_t)(M * N) * dtype_size(out_dtype),
-                                cudaMemcpyDeviceToHost, st));
-    return BW_OK;
+    rc = bw_qmatmul(x_dev, x_dtype, M, N, K, qweight, scale, zero_point, bias, out_dev, out_dtype,
+                    bits, group_size, workspace, workspace_bytes, stream);
+    if (rc != BW_OK) return rc;
+    return staging_copy(out_host, out_dev, (size_t)(M * N) * dtype_size(out_dtype), cudaMemcpyDeviceToHost, st);
 }
 
 int bw_qmatmul_grad_input(const void *grad_out, int grad_dtype, int64_t M, int64_t N, int64_t K,

@@ -234,6 +234,11 @@ BW_API size_t bw_qmatmul_noalloc_max_scratch_bytes(void);
  * copies x to `x_dev`, runs bw_qmatmul, copies the result from `out_dev` to `out_host`, all
  * asynchronously on `stream`.  The packed weights stay resident on the device.  This is the
  * end-to-end call timed by the benchmark (host<->device copies inside the timed region).
+ * Transfers of up to 4 MiB between 16-byte aligned buffers, the host one pinned, are made by a
+ * small copy kernel through the pinned buffer's device mapping (no copy-engine set-up per
+ * transfer, launch overlapped with the preceding kernel); anything else by cudaMemcpyAsync.
+ * As with any asynchronous copy, the host may reuse x_host / read out_host only after the
+ * stream has reached this call's end (event or synchronize).
  */
 BW_API int bw_qmatmul_host(const void *x_host, int x_dtype, int64_t M, int64_t N, int64_t K,
                     const int32_t *qweight, const void *scale, const void *zero_point,

@@ -581,3 +581,39 @@ def test_grad_input_tensor_core_kernel_vs_oracle(bits, g, gdt, shape):
     full = go.to(DEV).float() @ w
     slack = 2.0 ** -8 * full.abs() if gdt == torch.bfloat16 else 0.0
     assert bool(((gi.float() - full).abs() <= 1e-2 * rms(as_f32(full)) + slack).all())
+
+
+@pytest.mark.parametrize("pinned", [True, False])
+@pytest.mark.parametrize("M,N,K,bits,g", [(1, 1024, 4096, 4, 128), (16, 4096, 4096, 4, 128), (5, 72, 256, 8, 32),
+                                          (200, 512, 1024, 2, 64)])
+def test_host_buffer_call_equals_device_call(pinned, M, N, K, bits, g):
+    """bw_qmatmul_host (pinned buffers staged by the copy kernel, pageable ones by the copy engine)
+    returns exactly what the device-buffer call returns, also when replayed from a CUDA graph."""
+    from bitween_b200.kernels.cuda_loader import quantized_matmul_cuda, quantized_matmul_host
+    w = torch.from_numpy(synth.normal(31, (N, K), 0.02)).to(DEV)
+    q, s, z = _rtn_launch(w, bits, g, torch.float16, torch.float16, True)
+    bias = torch.from_numpy(synth.normal(32, (N,), 0.02)).to(DEV).half()
+    x = torch.from_numpy(synth.normal(33, (M, K), 1.0)).to(torch.bfloat16)
+    hx = x.clone().pin_memory() if pinned else x.clone()
+    hy = torch.zeros(M, N, dtype=torch.float16)
+    hy = hy.pin_memory() if pinned else hy
+    x_dev = torch.empty(M, K, dtype=torch.bfloat16, device=DEV)
+    out_dev = torch.empty(M, N, dtype=torch.float16, device=DEV)
+    want = quantized_matmul_cuda(x.to(DEV), q, s, z, bias, bits, g).cpu()
+    quantized_matmul_host(hx, q, s, z, bias, bits, g, hy, x_dev, out_dev)
+    torch.cuda.synchronize()
+    assert torch.equal(hy, want)
+    if pinned:
+        # new inputs through the same pinned buffer, the calls replayed from a graph
+        x2 = torch.from_numpy(synth.normal(34, (M, K), 1.0)).to(torch.bfloat16)
+        want2 = quantized_matmul_cuda(x2.to(DEV), q, s, z, bias, bits, g).cpu()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            quantized_matmul_host(hx, q, s, z, bias, bits, g, hy, x_dev, out_dev)
+        hx.copy_(x2)
+        hy.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(hy, want2)
+    assert _lib.lib().bw_device_status() == 0
