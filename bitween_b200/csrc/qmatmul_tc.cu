@@ -196,6 +196,10 @@ struct TcParams {
     int w_stages_log2;
     int splits;         // split-K factor = cluster size along grid z
     int kper;           // k-stages per split
+    int n_tiles;        // row tiles (N / 128, rounded up)
+    int tiles;          // output tiles: n_tiles x token tiles
+    int persistent;     // 1: grid.x CTAs walk the tile list (tile = blockIdx.x, += gridDim.x); 0: one tile per CTA
+    int tma_store;      // 1: output blocks leave through a shared-memory staging tile and TMA stores
     int x_is_bf16;      // always 0: kind::f16 MMAs take both operands in one 16-bit format
     Epilogue ep;        // activation / residual add on the way out
 };
@@ -243,9 +247,10 @@ __device__ __forceinline__ void expand_stage(const uint32_t (&w)[StageGeom<BITS>
     }
 }
 
-template <int BITS>
+template <int BITS, bool PERSIST, bool TMAST>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, const TcParams p) {
+qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
+              const __grid_constant__ CUtensorMap out_map, const TcParams p) {
     using SG = StageGeom<BITS>;
     // one slot of the packed-word ring: 128 rows x 128 bytes (SPS k-stages), 128-byte swizzle; whole
     // 128-byte row segments keep the DRAM accesses of the weight stream efficient
@@ -256,19 +261,28 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
     const int bn = p.bn, NSX = p.x_stages, NSW = p.w_stages;
     unsigned char *x_tiles = smem;                                        // [NSX][bn][128 B]         activations
     unsigned char *w_tiles = x_tiles + (size_t)NSX * bn * 128;            // [NSW][128][128 B]        packed words
-    uint64_t *bars = reinterpret_cast<uint64_t *>(w_tiles + (size_t)NSW * W_STAGE_BYTES);
+    // output staging of the TMA-store epilogue: per dequantization group one block [32 tokens][128 rows]
+    unsigned char *o_stage = w_tiles + (size_t)NSW * W_STAGE_BYTES;
+    const int o_esize = p.out_dtype == BW_F32 ? 4 : 2;
+    const size_t o_bytes = TMAST ? (size_t)TC_DQ_GROUPS * 32 * TC_BM * o_esize : 0;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(o_stage + o_bytes);
     uint64_t *a_full = bars, *a_empty = bars + TC_STAGES, *x_full = bars + 2 * TC_STAGES;
-    uint64_t *w_full = x_full + NSX, *w_empty = w_full + NSW, *acc_full = w_empty + NSW;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+    uint64_t *w_full = x_full + NSX, *w_empty = w_full + NSW, *acc_full = w_empty + NSW, *acc_empty = acc_full + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * TC_BM;
-    const int m0 = blockIdx.y * bn;
+    // Tile schedule.  Persistent launches (no split-K) walk the list tile = mt * n_tiles + nt from
+    // blockIdx.x in steps of gridDim.x: barriers, rings and tensor memory are set up once, the
+    // producer runs ahead into the next tile while the current one drains, and only the epilogue
+    // separates the MMAs of consecutive tiles.  Otherwise a CTA owns the tile its block index names.
+    const int first_tile = PERSIST ? (int)blockIdx.x : (int)(blockIdx.y * p.n_tiles + blockIdx.x);
+    const int tile_step = PERSIST ? (int)gridDim.x : p.tiles;
     // split-K over the CTAs of a cluster (grid z): this CTA owns k-stages [kt0, kt1)
     const int kt0 = blockIdx.z * p.kper;
     const int kt1 = min(kt0 + p.kper, p.k_stages);
     const int nk = max(kt1 - kt0, 0);
+    const int nslots = (nk + SG::SPS - 1) / SG::SPS;   // packed-word slots per tile of this CTA's k range
     // tensor memory: the accumulator (bn columns) followed by TC_STAGES tiles of dequantized
     // weights (the A operand: 128 lanes x 32 columns = 128 rows x 64 fp16 each)
     const uint32_t acc_cols = bn < 32 ? 32u : (uint32_t)bn;
@@ -280,6 +294,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
         for (int s = 0; s < NSX; ++s) mbar_init(&x_full[s], 1);
         for (int s = 0; s < NSW; ++s) { mbar_init(&w_full[s], 1); mbar_init(&w_empty[s], SG::SPS * 4); }   // w_empty: 4 reader warps per k-stage of the slot
         mbar_init(acc_full, 1);
+        mbar_init(acc_empty, TC_DQ_GROUPS * 4);          // every epilogue warp has read its part of the accumulator
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async_smem();
@@ -295,40 +310,50 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
         // (the small packed-word stages are freed by the dequantization warps as soon as they
         // have been read into registers, so this ring runs far ahead of the tensor core)
         if (lane == 0) {
-            const int nslots = (nk + SG::SPS - 1) / SG::SPS;   // packed-word slots of this CTA's k range
-            int ix = 0, iw = 0;
             int sx = 0, sw = 0;                     // ring slots and phases advance without divisions
             unsigned phx = 0, phw = 0, idle = 0;
-            while (ix < nk || iw < nslots) {
-                bool progressed = false;
-                if (iw < nslots) {
-                    const int s = sw;
-                    if (mbar_try_wait(&w_empty[s], phw ^ 1u)) {
-                        mbar_expect_tx(&w_full[s], (unsigned)W_STAGE_BYTES);
-                        tma_load_2d(w_tiles + (size_t)s * W_STAGE_BYTES, &w_map, (kt0 + iw * SG::SPS) * SG::WPS, n0, &w_full[s]);
-                        ++iw;
-                        if (++sw == NSW) { sw = 0; phw ^= 1u; }
-                        progressed = true;
+            int gx = 0;                             // activation stages requested so far, over all tiles
+            bool alive = true;
+            int t = first_tile;
+            do {   // (one trip, known at compile time, when not persistent)
+                const int n0 = (t % p.n_tiles) * TC_BM, m0 = (t / p.n_tiles) * bn;
+                int ix = 0, iw = 0;
+                while (ix < nk || iw < nslots) {
+                    bool progressed = false;
+                    if (iw < nslots) {
+                        const int s = sw;
+                        if (mbar_try_wait(&w_empty[s], phw ^ 1u)) {
+                            {
+                            mbar_expect_tx(&w_full[s], (unsigned)W_STAGE_BYTES);
+                            tma_load_2d(w_tiles + (size_t)s * W_STAGE_BYTES, &w_map, (kt0 + iw * SG::SPS) * SG::WPS, n0, &w_full[s]);
+                            }
+                            ++iw;
+                            if (++sw == NSW) { sw = 0; phw ^= 1u; }
+                            progressed = true;
+                        }
                     }
-                }
-                if (ix < nk) {
-                    const int s = sx;
-                    // the slot is free once the MMAs of stage ix - NSX have completed: that is the
-                    // commit that also frees the A stage of that k-stage (one commit per stage)
-                    const int jf = ix - NSX;
-                    if (jf < 0 || mbar_try_wait(&a_empty[jf % TC_STAGES], (unsigned)(jf / TC_STAGES) & 1u)) {
-                        mbar_expect_tx(&x_full[s], (unsigned)bn * 128u);
-                        tma_load_2d(x_tiles + (size_t)s * bn * 128, &x_map, (kt0 + ix) * TC_BK, m0, &x_full[s]);
-                        ++ix;
-                        if (++sx == NSX) { sx = 0; phx ^= 1u; }
-                        progressed = true;
+                    if (ix < nk) {
+                        const int s = sx;
+                        // the slot is free once the MMAs of the stage NSX positions back have completed:
+                        // that is the commit that also frees the A stage of that k-stage (one per stage)
+                        const int jf = gx - NSX;
+                        if (jf < 0 || mbar_try_wait(&a_empty[jf % TC_STAGES], (unsigned)(jf / TC_STAGES) & 1u)) {
+                            {
+                            mbar_expect_tx(&x_full[s], (unsigned)bn * 128u);
+                            tma_load_2d(x_tiles + (size_t)s * bn * 128, &x_map, (kt0 + ix) * TC_BK, m0, &x_full[s]);
+                            }
+                            ++ix;
+                            ++gx;
+                            if (++sx == NSX) { sx = 0; phx ^= 1u; }
+                            progressed = true;
+                        }
                     }
+                    if (progressed) { idle = 0; continue; }
+                    if (*abort_flag) { alive = false; break; }
+                    // (no sleep between polls: this single thread is what keeps both rings full)
+                    if (++idle > 64u * TC_WAIT_LIMIT) { *abort_flag = 1; atomicExch(&g_tc_status, 1); alive = false; break; }
                 }
-                if (progressed) { idle = 0; continue; }
-                if (*abort_flag) break;
-                __nanosleep(20);
-                if (++idle > TC_WAIT_LIMIT) { *abort_flag = 1; atomicExch(&g_tc_status, 1); break; }
-            }
+            } while (PERSIST && alive && (t += tile_step) < p.tiles);
         }
     } else if (warp == 1) {
         // ---- MMA issuer ----
@@ -339,134 +364,211 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
         // the pace of the kernel.
         const uint32_t idesc = umma_idesc_f16(bn, 0);
         bool ok = true;
-        int si = 0;
+        int si = 0, gi = 0, tile_iter = 0;          // gi: k-stages issued so far, over all tiles
         unsigned phx = 0;
-        for (int i = 0; i < nk && ok; ++i) {
-            const int sa = i % TC_STAGES;
-            const bool got = mbar_wait(&a_full[sa], (unsigned)(i / TC_STAGES) & 1u, abort_flag, 2) &&
-                             mbar_wait(&x_full[si], phx, abort_flag, 3);
-            ok = __all_sync(0xffffffffu, got);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t a_taddr = tmem_base + acc_cols + (uint32_t)sa * (TC_BK / 2);
-            const uint32_t b_addr = smem_addr(x_tiles + (size_t)si * bn * 128);
+        int t = first_tile;
+        do {
+            if (PERSIST && tile_iter > 0) {
+                // the epilogue warps have read the previous tile's sums out of the accumulator
+                ok = __all_sync(0xffffffffu, mbar_wait(acc_empty, (unsigned)(tile_iter - 1) & 1u, abort_flag, 7));
+                if (!ok) break;
+                tc_fence_after();
+            }
+            for (int i = 0; i < nk && ok; ++i, ++gi) {
+                const int sa = gi % TC_STAGES;
+                const bool got = mbar_wait(&a_full[sa], (unsigned)(gi / TC_STAGES) & 1u, abort_flag, 2) &&
+                                 mbar_wait(&x_full[si], phx, abort_flag, 3);
+                ok = __all_sync(0xffffffffu, got);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_taddr = tmem_base + acc_cols + (uint32_t)sa * (TC_BK / 2);
+                const uint32_t b_addr = smem_addr(x_tiles + (size_t)si * bn * 128);
 #pragma unroll
-            for (int k4 = 0; k4 < TC_BK / 16; ++k4)
-                umma_f16_ts(tmem_base, a_taddr + k4 * 8, umma_smem_desc(b_addr + k4 * 32), idesc,
-                            (i | k4) != 0 ? 1u : 0u);
-            umma_commit(&a_empty[sa]);     // the A stage and the activation slot are free once these MMAs have read them
-            if (++si == NSX) { si = 0; phx ^= 1u; }
-        }
-        if (ok) umma_commit(acc_full);     // accumulator complete (arrives at once when nk == 0)
+                for (int k4 = 0; k4 < TC_BK / 16; ++k4)
+                    umma_f16_ts(tmem_base, a_taddr + k4 * 8, umma_smem_desc(b_addr + k4 * 32), idesc,
+                                (i | k4) != 0 ? 1u : 0u);
+                umma_commit(&a_empty[sa]);     // the A stage and the activation slot are free once these MMAs have read them
+                if (++si == NSX) { si = 0; phx ^= 1u; }
+            }
+            if (ok) umma_commit(acc_full);     // accumulator complete (arrives at once when nk == 0)
+            ++tile_iter;
+        } while (PERSIST && ok && (t += tile_step) < p.tiles);
     } else {
         // ---- dequantization threads (one weight row each), then epilogue ----
         const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
-        const int dgroup = (warp - 2) >> 2;              // this group expands stages dgroup, dgroup+G, ...
+        const int dgroup = (warp - 2) >> 2;              // this group expands the stages whose running index is dgroup mod 4
         const int row = quad * 32 + lane;                // tile row == TMEM lane
-        int64_t n = (int64_t)n0 + row;
-        const bool n_ok = n < p.N;
-        if (!n_ok) n = p.N - 1;
-        const __half *srow = p.scale + n * p.G, *zrow = p.zp + n * p.G;
         const int gps = max(1, TC_BK >> p.g_shift);      // groups per stage (<= 4)
-
-        GroupConst gcs[4];
-        auto prefetch_consts = [&](int kt) {             // kt = global k-stage index
-            const int grp0 = (kt * TC_BK) >> p.g_shift;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if (i < gps) {
-                    const int grp = min(grp0 + i, p.G - 1);
-                    gcs[i].s2 = h2_as_u32(__half2half2(__ldg(srow + grp)));
-                    gcs[i].z1024 = h2_as_u32(__hadd2(__half2half2(__ldg(zrow + grp)), __float2half2_rn(1024.0f)));
-                } else {
-                    gcs[i] = gcs[0];
-                }
-            }
-        };
-        if (dgroup < nk) prefetch_consts(kt0 + dgroup);
-        bool ok = true;
         const int swz = (row & 7);                       // 128-byte swizzle of the packed-word slots
-        for (int i = dgroup; i < nk; i += TC_DQ_GROUPS) {
-            const int sa = i % TC_STAGES;
-            const int kt = kt0 + i;
-            GroupConst gc_now[4] = {gcs[0], gcs[1], gcs[2], gcs[3]};
-            if (i + TC_DQ_GROUPS < nk) prefetch_consts(kt + TC_DQ_GROUPS);
-            uint32_t w[SG::WPS];
-            {
-                // stage i lies in slot i / SPS of this CTA, at position (i % SPS) of each 128-byte row
-                const int slot = i / SG::SPS, si = slot & (NSW - 1);
-                const unsigned phw = (unsigned)(slot >> p.w_stages_log2) & 1u;
-                ok = __all_sync(0xffffffffu, mbar_wait(&w_full[si], phw, abort_flag, 6));
-                if (!ok) break;
-                const uint4 *src = reinterpret_cast<const uint4 *>(w_tiles + (size_t)si * W_STAGE_BYTES + (size_t)row * 128);
-                const int c0 = (i % SG::SPS) * SG::VPS;
+        bool ok = true;
+        int gbase = 0, slot_base = 0, tile_iter = 0;     // running stage / slot index of the tile's first stage
+        int t = first_tile;
+        do {
+            const int n0 = (t % p.n_tiles) * TC_BM, m0 = (t / p.n_tiles) * bn;
+            int64_t n = (int64_t)n0 + row;
+            const bool n_ok = n < p.N;
+            if (!n_ok) n = p.N - 1;
+            const __half *srow = p.scale + n * p.G, *zrow = p.zp + n * p.G;
+
+            GroupConst gcs[4];
+            auto prefetch_consts = [&](int kt) {             // kt = global k-stage index
+                const int grp0 = (kt * TC_BK) >> p.g_shift;
 #pragma unroll
-                for (int v = 0; v < SG::VPS; ++v) {
-                    const uint4 t = src[(c0 + v) ^ swz];
-                    w[4 * v] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
+                for (int i = 0; i < 4; ++i) {
+                    if (i < gps) {
+                        const int grp = min(grp0 + i, p.G - 1);
+                        gcs[i].s2 = h2_as_u32(__half2half2(__ldg(srow + grp)));
+                        gcs[i].z1024 = h2_as_u32(__hadd2(__half2half2(__ldg(zrow + grp)), __float2half2_rn(1024.0f)));
+                    } else {
+                        gcs[i] = gcs[0];
+                    }
                 }
-                // generic-proxy reads of the slot must be ordered before the async-proxy (TMA) write
-                // that refills it: without this fence random rows read the next stage's words
-                fence_proxy_async_smem();
+            };
+            const int i0 = (dgroup - gbase) & (TC_DQ_GROUPS - 1);   // this group's first stage of the tile
+            if (i0 < nk) prefetch_consts(kt0 + i0);
+            for (int i = i0; i < nk; i += TC_DQ_GROUPS) {
+                const int gi = gbase + i;
+                const int sa = gi % TC_STAGES;
+                const int kt = kt0 + i;
+                GroupConst gc_now[4] = {gcs[0], gcs[1], gcs[2], gcs[3]};
+                if (i + TC_DQ_GROUPS < nk) prefetch_consts(kt + TC_DQ_GROUPS);
+                uint32_t w[SG::WPS];
+                {
+                    // stage i lies in slot i / SPS of this tile, at position (i % SPS) of each 128-byte row
+                    const int slot = slot_base + i / SG::SPS, si = slot & (NSW - 1);
+                    const unsigned phw = (unsigned)(slot >> p.w_stages_log2) & 1u;
+                    ok = __all_sync(0xffffffffu, mbar_wait(&w_full[si], phw, abort_flag, 6));
+                    if (!ok) break;
+                    const uint4 *src = reinterpret_cast<const uint4 *>(w_tiles + (size_t)si * W_STAGE_BYTES + (size_t)row * 128);
+                    const int c0 = (i % SG::SPS) * SG::VPS;
+#pragma unroll
+                    for (int v = 0; v < SG::VPS; ++v) {
+                        const uint4 tq = src[(c0 + v) ^ swz];
+                        w[4 * v] = tq.x; w[4 * v + 1] = tq.y; w[4 * v + 2] = tq.z; w[4 * v + 3] = tq.w;
+                    }
+                    // generic-proxy reads of the slot must be ordered before the async-proxy (TMA) write
+                    // that refills it: without this fence random rows read the next stage's words
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&w_empty[si]);    // the packed words are in registers now
+                }
+                uint4 chunk[8];
+                if (gps == 1) expand_stage<BITS, true>(w, gc_now, kt * TC_BK, p.g_shift, (kt * TC_BK) >> p.g_shift, chunk);
+                else expand_stage<BITS, false>(w, gc_now, kt * TC_BK, p.g_shift, (kt * TC_BK) >> p.g_shift, chunk);
+                ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[sa], ((unsigned)(gi / TC_STAGES) & 1u) ^ 1u, abort_flag, 4));
+                if (!ok) break;
+                tc_fence_after();                            // the MMAs that read this stage come before the stores below
+                {
+                    // this thread's row of the A tile: 64 fp16 in k order = 32 columns of its TMEM lane
+                    uint32_t a_regs[32];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) { a_regs[4 * c] = chunk[c].x; a_regs[4 * c + 1] = chunk[c].y; a_regs[4 * c + 2] = chunk[c].z; a_regs[4 * c + 3] = chunk[c].w; }
+                    tmem_st_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc_cols + (uint32_t)sa * (TC_BK / 2), a_regs);
+                }
+                tc_fence_before();                           // the stores are ordered before the arrival
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&w_empty[slot & (NSW - 1)]);    // the packed words are in registers now
+                if (lane == 0) mbar_arrive(&a_full[sa]);
             }
-            uint4 chunk[8];
-            if (gps == 1) expand_stage<BITS, true>(w, gc_now, kt * TC_BK, p.g_shift, (kt * TC_BK) >> p.g_shift, chunk);
-            else expand_stage<BITS, false>(w, gc_now, kt * TC_BK, p.g_shift, (kt * TC_BK) >> p.g_shift, chunk);
-            ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[sa], ((unsigned)(i / TC_STAGES) & 1u) ^ 1u, abort_flag, 4));
-            if (!ok) break;
-            tc_fence_after();                            // the MMAs that read this stage come before the stores below
-            {
-                // this thread's row of the A tile: 64 fp16 in k order = 32 columns of its TMEM lane
-                uint32_t a_regs[32];
+            // ---- epilogue of this tile ----
+            const bool acc_ok = __all_sync(0xffffffffu, ok && mbar_wait(acc_full, (unsigned)tile_iter & 1u, abort_flag, 5));
+            if (acc_ok) tc_fence_after();
+            const int nblk = bn < 32 ? 1 : bn / 32, per = (nblk + TC_DQ_GROUPS - 1) / TC_DQ_GROUPS;
+            const __half bias_h = (p.bias && n_ok) ? p.bias[n] : __float2half(0.0f);
+            auto store_out = [&](int64_t m, float v) {
+                store_output(p.out, p.out_dtype, m * p.N + n, v, p.bias != nullptr, bias_h, p.ep);
+            };
+            if (p.splits == 1) {
+                if (TMAST && acc_ok) {
+                    // Each group turns its blocks of 32 tokens into [32 tokens][128 rows] tiles of the output
+                    // dtype in shared memory (lane = row: consecutive lanes write consecutive elements) and
+                    // one thread hands each tile to a TMA store, which writes whole 256- or 512-byte row
+                    // segments and clips at the edges of the output.  (Two-byte stores straight from the
+                    // registers, 64 bytes per warp instruction, took 9 us of a 35 us tile.)
+                    unsigned char *stage = o_stage + (size_t)dgroup * 32 * TC_BM * o_esize;
+                    const bool issuer = quad == 0 && lane == 0;
+                    const int cb_end = min(nblk, (dgroup + 1) * per);
+                    for (int cb = dgroup * per; cb < cb_end; ++cb) {
+                        uint32_t r[32];
+                        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), r);
+                        if (cb == cb_end - 1) {
+                            // this warp's last read of the accumulator: the next tile's first MMA may overwrite it
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(acc_empty);
+                        }
+                        // the previous store out of this staging tile has finished reading it
+                        if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                        asm volatile("bar.sync %0, 128;" ::"r"(1 + dgroup) : "memory");
+                        if (p.out_dtype == BW_F16) {
+                            __half *dst = reinterpret_cast<__half *>(stage) + row;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) { a_regs[4 * c] = chunk[c].x; a_regs[4 * c + 1] = chunk[c].y; a_regs[4 * c + 2] = chunk[c].z; a_regs[4 * c + 3] = chunk[c].w; }
-                tmem_st_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc_cols + (uint32_t)sa * (TC_BK / 2), a_regs);
-            }
-            tc_fence_before();                           // the stores are ordered before the arrival
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&a_full[sa]);
-        }
-        // ---- epilogue ----
-        const bool acc_ok = __all_sync(0xffffffffu, ok && mbar_wait(acc_full, 0u, abort_flag, 5));
-        if (acc_ok) tc_fence_after();
-        const int nblk = bn < 32 ? 1 : bn / 32, per = (nblk + TC_DQ_GROUPS - 1) / TC_DQ_GROUPS;
-        const __half bias_h = (p.bias && n_ok) ? p.bias[n] : __float2half(0.0f);
-        auto store_out = [&](int64_t m, float v) {
-            store_output(p.out, p.out_dtype, m * p.N + n, v, p.bias != nullptr, bias_h, p.ep);
-        };
-        if (p.splits == 1) {
-            if (acc_ok) {
-                // the warp groups share the lane quadrants and split the token columns
-                for (int cb = dgroup * per; cb < min(nblk, (dgroup + 1) * per); ++cb) {
-                    uint32_t r[32];
-                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), r);
+                            for (int j = 0; j < 32; ++j) {
+                                __half c = __float2half_rn(__uint_as_float(r[j]));       // the GEMM's fp16 output rounding
+                                if (p.bias) c = __hadd(c, bias_h);                       // separate fp16 bias add
+                                if (p.ep.act == BW_ACT_RELU) c = __hmax(c, __float2half(0.0f));
+                                dst[j * TC_BM] = c;
+                            }
+                        } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int64_t m = (int64_t)m0 + cb * 32 + j;
-                        if (n_ok && m < p.M) store_out(m, __uint_as_float(r[j]));
+                            for (int j = 0; j < 32; ++j) {
+                                float v = __uint_as_float(r[j]);
+                                if (p.bias) v += __half2float(bias_h);
+                                if (p.ep.act == BW_ACT_RELU) v = fmaxf(v, 0.0f);
+                                if (p.out_dtype == BW_BF16) reinterpret_cast<__nv_bfloat16 *>(stage)[j * TC_BM + row] = __float2bfloat16_rn(v);
+                                else reinterpret_cast<float *>(stage)[j * TC_BM + row] = v;
+                            }
+                        }
+                        fence_proxy_async_smem();                  // generic-proxy writes before the async-proxy read
+                        asm volatile("bar.sync %0, 128;" ::"r"(1 + dgroup) : "memory");
+                        if (issuer) {
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                                         ::"l"(&out_map), "r"(smem_addr(stage)), "r"(n0), "r"(m0 + cb * 32) : "memory");
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        }
+                    }
+                    if (cb_end <= dgroup * per) {
+                        // a group without a block of this tile still owes its arrivals
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_empty);
+                    }
+                } else if (acc_ok) {
+                    // the warp groups share the lane quadrants and split the token columns
+                    for (int cb = dgroup * per; cb < min(nblk, (dgroup + 1) * per); ++cb) {
+                        uint32_t r[32];
+                        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), r);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int64_t m = (int64_t)m0 + cb * 32 + j;
+                            if (n_ok && m < p.M) store_out(m, __uint_as_float(r[j]));
+                        }
+                    }
+                    // the accumulator may be overwritten by the next tile's first MMA
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_empty);
+                }
+            } else {
+                // split-K: park this CTA's partial tile in its own shared memory (the input ring
+                // is idle by now) as red[column][row]; the cluster sums it below
+                float *red = reinterpret_cast<float *>(x_tiles);
+                if (acc_ok) {
+                    for (int cb = dgroup * per; cb < min(nblk, (dgroup + 1) * per); ++cb) {
+                        uint32_t r[32];
+                        if (nk > 0) tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), r);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) red[(cb * 32 + j) * TC_BM + row] = nk > 0 ? __uint_as_float(r[j]) : 0.0f;
                     }
                 }
             }
-        } else {
-            // split-K: park this CTA's partial tile in its own shared memory (the input ring
-            // is idle by now) as red[column][row]; the cluster sums it below
-            float *red = reinterpret_cast<float *>(x_tiles);
-            if (acc_ok) {
-                for (int cb = dgroup * per; cb < min(nblk, (dgroup + 1) * per); ++cb) {
-                    uint32_t r[32];
-                    if (nk > 0) tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), r);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) red[(cb * 32 + j) * TC_BM + row] = nk > 0 ? __uint_as_float(r[j]) : 0.0f;
-                }
-            }
-        }
+            if (!acc_ok) break;
+            ++tile_iter; gbase += nk; slot_base += nslots;
+        } while (PERSIST && (t += tile_step) < p.tiles);
     }
     if (p.splits > 1) {
         // every thread of every CTA of the cluster reaches these barriers (also after an abort)
         cgx::cluster_group cluster = cgx::this_cluster();
         float *red = reinterpret_cast<float *>(x_tiles);
+        const int n0 = blockIdx.x * TC_BM, m0 = blockIdx.y * bn;     // split-K launches are never persistent
         cluster.sync();
         if (warp >= 2 && *abort_flag == 0) {
             const int rank = (int)cluster.block_rank(), nranks = (int)cluster.num_blocks();
@@ -485,6 +587,8 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
         }
         cluster.sync();   // keep shared memory alive until every peer has read it
     }
+    // the staging tiles must outlive the bulk stores that read them
+    if (TMAST) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
@@ -523,11 +627,12 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 template <int BITS>
-int launch_tc(const CUtensorMap &xmap, const CUtensorMap &wmap, TcParams p, cudaStream_t st) {
+int launch_tc(const CUtensorMap &xmap, const CUtensorMap &wmap, const CUtensorMap &omap, TcParams p, cudaStream_t st) {
     using SG = StageGeom<BITS>;
-    auto kern = qmm_tc_kernel<BITS>;
+    // (the kernel is chosen below, once the schedule is known)
     const size_t w_stage = (size_t)TC_BM * 128, x_stage = (size_t)p.bn * 128;
-    const size_t fixed = 1024 /*alignment slack*/ + 1024 /*barriers*/;
+    const size_t o_stage = p.tma_store ? (size_t)TC_DQ_GROUPS * 32 * TC_BM * (p.out_dtype == BW_F32 ? 4 : 2) : 0;
+    const size_t fixed = 1024 /*alignment slack*/ + 1024 /*barriers*/ + o_stage;
     // Packed-word ring: 4 slots of 16 KB for small token tiles (the weight stream is what is being
     // waited for), 2 for large ones.  Each slot is always read by the same dequantization groups,
     // once per phase (a waiter that skipped a phase could not tell phase k from phase k-2).
@@ -550,18 +655,36 @@ int launch_tc(const CUtensorMap &xmap, const CUtensorMap &wmap, TcParams p, cuda
     }
     const size_t red_bytes = (size_t)(p.bn < 32 ? 32 : p.bn) * TC_BM * 4;
     if (splits > 8 || p.bn > 128 || red_bytes > (size_t)nsx * x_stage + (size_t)nsw * w_stage) splits = 1;
+    if (splits > 1) p.tma_store = 0;   // split-K tiles are summed by the cluster and stored from registers
     p.splits = splits;
     p.kper = (p.k_stages + splits - 1) / splits;
+    if (tiles > ((int64_t)1 << 30)) return BW_ERR_UNSUPPORTED;
+    p.n_tiles = (int)((p.N + TC_BM - 1) / TC_BM);
+    p.tiles = (int)tiles;
+    // More tiles than SMs: one persistent CTA per SM walks the tile list (whole packed-word slots per
+    // tile, so that every slot of the ring collects its full count of releases).
+    int sms = 148;
+    {
+        int dev_id = 0, v = 0;
+        if (cudaGetDevice(&dev_id) == cudaSuccess &&
+            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev_id) == cudaSuccess && v > 0)
+            sms = v;
+    }
+    p.persistent = (splits == 1 && tiles > sms && p.k_stages % SG::SPS == 0) ? 1 : 0;
     const size_t smem = fixed + (size_t)nsx * x_stage + (size_t)nsw * w_stage;
     static size_t configured[64] = {};
     int dev = 0;
     BW_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || smem > configured[dev]) {
-        BW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        BW_CUDA_TRY(cudaFuncSetAttribute(qmm_tc_kernel<BITS, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        BW_CUDA_TRY(cudaFuncSetAttribute(qmm_tc_kernel<BITS, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        BW_CUDA_TRY(cudaFuncSetAttribute(qmm_tc_kernel<BITS, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        BW_CUDA_TRY(cudaFuncSetAttribute(qmm_tc_kernel<BITS, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((p.N + TC_BM - 1) / TC_BM), (unsigned)((p.M + p.bn - 1) / p.bn), (unsigned)splits);
+    cfg.gridDim = p.persistent ? dim3((unsigned)sms, 1, 1)
+                               : dim3((unsigned)p.n_tiles, (unsigned)((p.M + p.bn - 1) / p.bn), (unsigned)splits);
     cfg.blockDim = dim3(TC_THREADS, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -572,7 +695,10 @@ int launch_tc(const CUtensorMap &xmap, const CUtensorMap &wmap, TcParams p, cuda
     attr[0].val.clusterDim.z = (unsigned)splits;
     cfg.attrs = attr;
     cfg.numAttrs = splits > 1 ? 1 : 0;
-    BW_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, xmap, wmap, p));
+    if (p.persistent && p.tma_store) BW_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_tc_kernel<BITS, true, true>, xmap, wmap, omap, p));
+    else if (p.persistent) BW_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_tc_kernel<BITS, true, false>, xmap, wmap, omap, p));
+    else if (p.tma_store) BW_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_tc_kernel<BITS, false, true>, xmap, wmap, omap, p));
+    else BW_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_tc_kernel<BITS, false, false>, xmap, wmap, omap, p));
     return BW_OK;
 }
 
@@ -662,11 +788,28 @@ int qmatmul_tc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
                                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rw != CUDA_SUCCESS) return BW_ERR_UNSUPPORTED;
+    // output [M tokens][N]: boxes of 32 tokens x 128 rows for the TMA-store epilogue (needs a 16-byte
+    // aligned base and row pitch; a residual operand is read per element, so it takes the direct path)
+    CUtensorMap omap = wmap;
+    const size_t oes = dtype_size(out_dtype);
+    p.tma_store = 0;
+    // (only for tiles of 256 tokens: up to 128 tokens a thread stores at most 32 values, and the
+    // latency of the staged route outweighs them -- measured 8-14 % slower at 64 tokens)
+    if (p.bn == 256 && N >= TC_BM && (N * oes) % 16 == 0 && aligned_to(out, 16) && !p.ep.residual) {
+        const cuuint64_t odims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+        const cuuint64_t ostrides[1] = {(cuuint64_t)N * oes};
+        const cuuint32_t obox[2] = {(cuuint32_t)TC_BM, 32u};
+        const CUresult ro = encode_tiled_fn()(&omap, out_dtype == BW_F32 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16,
+                                              2, out, odims, ostrides, obox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (ro == CUDA_SUCCESS) p.tma_store = 1;
+    }
     set_last_kernel("qmm_tc_kernel");
     switch (bits) {
-        case 2: return launch_tc<2>(map, wmap, p, st);
-        case 4: return launch_tc<4>(map, wmap, p, st);
-        default: return launch_tc<8>(map, wmap, p, st);
+        case 2: return launch_tc<2>(map, wmap, omap, p, st);
+        case 4: return launch_tc<4>(map, wmap, omap, p, st);
+        default: return launch_tc<8>(map, wmap, omap, p, st);
     }
 }
 
