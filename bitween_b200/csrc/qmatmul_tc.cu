@@ -670,7 +670,10 @@ int launch_tc(const CUtensorMap &xmap, const CUtensorMap &wmap, const CUtensorMa
             cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev_id) == cudaSuccess && v > 0)
             sms = v;
     }
-    p.persistent = (splits == 1 && tiles > sms && p.k_stages % SG::SPS == 0) ? 1 : 0;
+    // (tiles of 256 tokens and K <= 4096 only: for smaller token tiles and for longer K the per-tile costs
+    // it removes are a small share, and the one-tile instantiation, with fewer registers, measured faster:
+    // 7 % on a 28672 x 8192 layer at 4096 tokens)
+    p.persistent = (splits == 1 && p.bn == 256 && p.k_stages <= 64 && tiles > sms && p.k_stages % SG::SPS == 0) ? 1 : 0;
     const size_t smem = fixed + (size_t)nsx * x_stage + (size_t)nsw * w_stage;
     static size_t configured[64] = {};
     int dev = 0;
