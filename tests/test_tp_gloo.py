@@ -27,7 +27,12 @@ def _layer(seed, N, K, bits, g, bias):
 
 
 def _oracle_matmul(x, qweight, scale, zero_point, bias, bits, group_size, **kw):
-    return oracle_forward(x.reshape(-1, x.shape[-1]), qweight, scale, zero_point, bias, bits, group_size)
+    x2 = x.reshape(-1, x.shape[-1])
+    if kw.get("out_dtype") == torch.float32:
+        # the library's fp32 output: the accumulator plus the bias, no 16-bit rounding
+        _, acc = oracle_forward(x2, qweight, scale, zero_point, None, bits, group_size, want_acc=True)
+        return acc if bias is None else acc + bias.float()
+    return oracle_forward(x2, qweight, scale, zero_point, bias, bits, group_size)
 
 
 def test_shards_equal_quantizing_the_sharded_weight():
@@ -77,6 +82,10 @@ def _worker(rank, world, port, ret):
         assert tuple(h.shape) == (5, 96 // world)
         y = row(torch.relu(h))                          # all-reduce inside
         tp.check_same_across_ranks(y.shape)
+        # fp32 partial sums on the wire, one fp16 rounding after the reduce
+        row32 = tp.RowParallelQuantizedLinear.from_full(down, rank, world, reduce_dtype=torch.float32)
+        y32 = row32(torch.relu(h))
+        assert y32.dtype == torch.float16 and y32.shape == y.shape
         # single-process reference of the same two layers
         h_full = _oracle_matmul(x, up.qweight, up.scale, up.zero_point, up.bias, 4, 64)
         y_full = _oracle_matmul(torch.relu(h_full), down.qweight, down.scale, down.zero_point, down.bias, 8, 16)
@@ -90,7 +99,8 @@ def _worker(rank, world, port, ret):
             mismatch_caught = False
         except RuntimeError:
             mismatch_caught = True
-        ret[rank] = (err, rms, ok_gather, mismatch_caught)
+        err32 = float((y32.float() - y_full.float()).abs().max())
+        ret[rank] = (err, rms, ok_gather, mismatch_caught, err32)
     finally:
         dist.destroy_process_group()
 
@@ -103,7 +113,9 @@ def test_two_rank_column_then_row_parallel_matches_single_process():
     mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
     assert len(ret) == world
     for rank in range(world):
-        err, rms, ok_gather, mismatch_caught = ret[rank]
+        err, rms, ok_gather, mismatch_caught, err32 = ret[rank]
         # partial sums are rounded to fp16 before the all-reduce: 1e-2 * RMS(output) bar
         assert err <= 1e-2 * rms, (rank, err, rms)
+        # with fp32 partials only the final rounding differs from the single-process result: one fp16 ulp
+        assert err32 <= max(2.0 ** -10 * 4 * rms, 1e-3 * rms), (rank, err32, rms)
         assert ok_gather and mismatch_caught
