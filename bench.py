@@ -430,6 +430,23 @@ def run_single_gpu_extras(args, torch, device, gen):
                 del x, y
             del L
         out[f"prefill_w{bits}g{g}_TFLOPs"] = pf
+    # gated feed-forward of a Llama-3-8B block in decode: gate and up as ONE [2 x 14336, 4096] GEMM with the
+    # SiLU * up epilogue, against two plain calls followed by torch's silu and mul
+    from bitween_b200.kernels.cuda_loader import interleave_gate_up
+    glu = {}
+    Fg, Kg = 14336, 4096
+    pairs = [(Layer(Fg, Kg, 4, 128, device, gen, torch, fn), Layer(Fg, Kg, 4, 128, device, gen, torch, fn)) for _ in range(3)]
+    fusedw = [(interleave_gate_up(a.q, b.q), interleave_gate_up(a.scale, b.scale), interleave_gate_up(a.zp, b.zp)) for a, b in pairs]
+    for M in (1, 16):
+        x = torch.randn(M, Kg, device=device, generator=gen).to(torch.bfloat16)
+        yf = torch.empty(M, Fg, device=device, dtype=torch.float16)
+        ms_f = graph_ms(torch, lambda: [qmm(x, q, s_, z, None, 4, 128, out=yf, activation="silu_mul") for (q, s_, z) in fusedw], flush) / len(fusedw)
+        ms_s = graph_ms(torch, lambda: [torch.nn.functional.silu(qmm(x, a.q, a.scale, a.zp, None, 4, 128)) *
+                                        qmm(x, b.q, b.scale, b.zp, None, 4, 128) for a, b in pairs], flush) / len(pairs)
+        glu[f"M{M}"] = {"fused_us": round(ms_f * 1e3, 2), "separate_us": round(ms_s * 1e3, 2),
+                        "fused_GBps": round(decode_bytes(M, 2 * Fg, Kg, 4, 128) / (ms_f * 1e-3) / 1e9, 1)}
+    out["gate_up_silu_mul_decode_w4g128"] = glu
+    del pairs, fusedw
     # backward of the frozen layer (grad_input = grad_output @ W, bitween/modules.py:108-141) at 4096 tokens
     from bitween_b200.kernels.cuda_loader import quantized_matmul_grad_input as qgrad
     gi = {}

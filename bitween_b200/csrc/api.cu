@@ -195,6 +195,9 @@ static int qmatmul_dispatch(const void *x, int x_dtype, int64_t M, int64_t N, in
     if (M == 0 || N == 0) return BW_OK;
     cudaStream_t st = (cudaStream_t)stream;
     const __half *s = (const __half *)scale, *z = (const __half *)zero_point, *b = (const __half *)bias;
+    // the gated epilogue pairs adjacent weight rows: only the decode and tensor-core kernels do that
+    const bool paired = g_epilogue.act == BW_ACT_SILU_MUL;
+    if (paired && (K == 0 || !smallm_fast_path_ok(x, x_dtype, K, qweight, bits, group_size))) return BW_ERR_UNSUPPORTED;
     if (K == 0) {
         // empty reduction: out = bias (or 0); run the general kernel, which handles it
         return qmatmul_smallm(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, nullptr, st);
@@ -205,13 +208,14 @@ static int qmatmul_dispatch(const void *x, int x_dtype, int64_t M, int64_t N, in
         if (!workspace || workspace_bytes < bw_qmatmul_workspace_bytes(M, N, K, bits, group_size))
             return BW_ERR_WORKSPACE;
         rc = qmatmul_decode(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, workspace, st);
-        if (rc != BW_ERR_UNSUPPORTED) return rc;   // otherwise nothing was launched: use the cluster split-K kernel
+        if (rc != BW_ERR_UNSUPPORTED || paired) return rc;   // otherwise nothing was launched: use the cluster split-K kernel
     }
     if (allow_tc && M > TC_MIN_TOKENS && tc_path_ok(M, N, K, qweight, bits, group_size)) {
         const bool direct = x_dtype == BW_F16 && aligned_to(x, 16);   // TMA reads fp16 activations as they are
         if (!direct && (!workspace || workspace_bytes < tc_workspace_bytes(M, K))) return BW_ERR_WORKSPACE;
         return qmatmul_tc(x, x_dtype, M, N, K, qweight, s, z, b, out, out_dtype, bits, group_size, workspace, st);
     }
+    if (paired) return BW_ERR_UNSUPPORTED;
     // token blocks of at most 64 through the streaming kernel
     if (!workspace || workspace_bytes < smallm_workspace_bytes(M < 64 ? M : 64, K, bits)) return BW_ERR_WORKSPACE;
     const size_t xs = dtype_size(x_dtype), os = dtype_size(out_dtype);
@@ -236,7 +240,8 @@ int bw_qmatmul_fused(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K
                      int bits, int group_size, const bw_epilogue *ep, void *workspace, size_t workspace_bytes,
                      void *stream) {
     if (ep) {
-        if (ep->activation != BW_ACT_NONE && ep->activation != BW_ACT_RELU) return BW_ERR_UNSUPPORTED;
+        if (ep->activation != BW_ACT_NONE && ep->activation != BW_ACT_RELU && ep->activation != BW_ACT_SILU_MUL) return BW_ERR_UNSUPPORTED;
+        if (ep->activation == BW_ACT_SILU_MUL && N % 4 != 0) return BW_ERR_SHAPE;
         if (!aligned_to(ep->residual, 2)) return BW_ERR_ALIGN;
         g_epilogue = {ep->activation, reinterpret_cast<const __half *>(ep->residual)};
     }

@@ -66,7 +66,7 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 // fp16 outputs reproduce the eager op-by-op result: fp16(acc), + bias, relu, + residual, each
 // rounded to fp16 like the separate torch ops would.
 struct Epilogue {
-    int act;                  // BW_ACT_NONE | BW_ACT_RELU
+    int act;                  // BW_ACT_NONE | BW_ACT_RELU | BW_ACT_SILU_MUL
     const __half *residual;   // [M, N] fp16, added last, or null
 };
 // The epilogue of the bw_qmatmul_fused call in progress on this thread (none otherwise).
@@ -83,6 +83,29 @@ __device__ __forceinline__ void store_output(void *out, int out_dtype, int64_t i
     } else {
         if (has_bias) v += __half2float(bias);
         if (ep.act == BW_ACT_RELU) v = fmaxf(v, 0.0f);
+        if (ep.residual) v += __half2float(ep.residual[idx]);
+        if (out_dtype == BW_BF16) reinterpret_cast<__nv_bfloat16 *>(out)[idx] = __float2bfloat16_rn(v);
+        else reinterpret_cast<float *>(out)[idx] = v;
+    }
+}
+
+
+// BW_ACT_SILU_MUL: the packed weight holds gate row i in row 2i and up row i in row 2i+1 (one
+// [2*ffn, K] GEMM for the gated feed-forward), and the output [M, N/2] is silu(gate) * up:
+// g = the two linears' outputs as the plain call would round them, silu evaluated in fp32 and
+// rounded like a torch op on an fp16 tensor, the product rounded once more, then the residual.
+__device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ void store_output_silu_mul(void *out, int out_dtype, int64_t idx, float g, float u, bool has_bias,
+                                                      __half bias_g, __half bias_u, const Epilogue &ep) {
+    if (out_dtype == BW_F16) {
+        __half gh = __float2half_rn(g), uh = __float2half_rn(u);
+        if (has_bias) { gh = __hadd(gh, bias_g); uh = __hadd(uh, bias_u); }
+        __half c = __hmul(__float2half_rn(silu_f32(__half2float(gh))), uh);
+        if (ep.residual) c = __hadd(c, ep.residual[idx]);
+        reinterpret_cast<__half *>(out)[idx] = c;
+    } else {
+        if (has_bias) { g += __half2float(bias_g); u += __half2float(bias_u); }
+        float v = silu_f32(g) * u;
         if (ep.residual) v += __half2float(ep.residual[idx]);
         if (out_dtype == BW_BF16) reinterpret_cast<__nv_bfloat16 *>(out)[idx] = __float2bfloat16_rn(v);
         else reinterpret_cast<float *>(out)[idx] = v;

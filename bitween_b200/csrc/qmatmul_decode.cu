@@ -413,6 +413,21 @@ qmm_decode_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_consta
             auto store_f4 = [&](int idx, float4 val) {           // idx: float4 index into the [MTOK][128] tile
                 const int e = idx * 4;
                 const int m = e / DK_ROWS, r = e % DK_ROWS;
+                if constexpr (EPI) {
+                    if (ep.act == BW_ACT_SILU_MUL) {
+                        // rows come in (gate, up) pairs: two outputs of the [M, N/2] result per float4
+                        if (m < p.M) {
+                            const int64_t n = nbase + r, half_n = p.N >> 1;
+                            if (n + 1 < p.N)
+                                store_output_silu_mul(p.out, p.out_dtype, m * half_n + (n >> 1), val.x, val.y, p.bias != nullptr,
+                                                      p.bias ? p.bias[n] : __half(), p.bias ? p.bias[n + 1] : __half(), ep);
+                            if (n + 3 < p.N)
+                                store_output_silu_mul(p.out, p.out_dtype, m * half_n + (n >> 1) + 1, val.z, val.w, p.bias != nullptr,
+                                                      p.bias ? p.bias[n + 2] : __half(), p.bias ? p.bias[n + 3] : __half(), ep);
+                        }
+                        return;
+                    }
+                }
                 if (m < p.M) {
                     if (nbase + r + 0 < p.N) store_out(m, nbase + r + 0, val.x);
                     if (nbase + r + 1 < p.N) store_out(m, nbase + r + 1, val.y);

@@ -536,6 +536,19 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
                     for (int cb = dgroup * per; cb < min(nblk, (dgroup + 1) * per); ++cb) {
                         uint32_t r[32];
                         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), r);
+                        if (p.ep.act == BW_ACT_SILU_MUL) {
+                            // adjacent lanes hold a (gate, up) row pair: the even lane takes both and stores
+                            const __half bias_u = __shfl_xor_sync(0xffffffffu, bias_h, 1);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const float up = __shfl_xor_sync(0xffffffffu, __uint_as_float(r[j]), 1);
+                                const int64_t m = (int64_t)m0 + cb * 32 + j;
+                                if ((lane & 1) == 0 && n + 1 < p.N && n_ok && m < p.M)
+                                    store_output_silu_mul(p.out, p.out_dtype, m * (p.N >> 1) + (n >> 1), __uint_as_float(r[j]), up,
+                                                          p.bias != nullptr, bias_h, bias_u, p.ep);
+                            }
+                            continue;
+                        }
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             const int64_t m = (int64_t)m0 + cb * 32 + j;
@@ -581,6 +594,14 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
                 float v = 0.0f;
                 for (int q = 0; q < nranks; ++q) v += cluster.map_shared_rank(red, q)[c * TC_BM + row];
                 const int64_t m = (int64_t)m0 + c;
+                if (p.ep.act == BW_ACT_SILU_MUL) {
+                    // (the loop bounds do not depend on the lane: the whole warp is here)
+                    const float up = __shfl_xor_sync(0xffffffffu, v, 1);
+                    const __half bias_u = __shfl_xor_sync(0xffffffffu, bias_h, 1);
+                    if ((lane & 1) == 0 && n + 1 < p.N && m < p.M)
+                        store_output_silu_mul(p.out, p.out_dtype, m * (p.N >> 1) + (n >> 1), v, up, p.bias != nullptr, bias_h, bias_u, p.ep);
+                    continue;
+                }
                 if (n < p.N && m < p.M)
                     store_output(p.out, p.out_dtype, m * p.N + n, v, p.bias != nullptr, bias_h, p.ep);
             }
@@ -798,7 +819,7 @@ int qmatmul_tc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
     p.tma_store = 0;
     // (only for tiles of 256 tokens: up to 128 tokens a thread stores at most 32 values, and the
     // latency of the staged route outweighs them -- measured 8-14 % slower at 64 tokens)
-    if (p.bn == 256 && N >= TC_BM && (N * oes) % 16 == 0 && aligned_to(out, 16) && !p.ep.residual) {
+    if (p.bn == 256 && N >= TC_BM && (N * oes) % 16 == 0 && aligned_to(out, 16) && !p.ep.residual && p.ep.act != BW_ACT_SILU_MUL) {
         const cuuint64_t odims[2] = {(cuuint64_t)N, (cuuint64_t)M};
         const cuuint64_t ostrides[1] = {(cuuint64_t)N * oes};
         const cuuint32_t obox[2] = {(cuuint32_t)TC_BM, 32u};

@@ -38,7 +38,7 @@ def dtype_code(dt):
         raise TypeError(f"bitween_b200: unsupported dtype {dt}") from None
 
 
-ACT_NONE, ACT_RELU = 0, 1
+ACT_NONE, ACT_RELU, ACT_SILU_MUL = 0, 1, 2
 
 
 class Epilogue(ctypes.Structure):

@@ -29,7 +29,9 @@ def quantized_matmul_cuda(x, qweight, scale, zero_point, bias, bits, group_size,
 
     `activation="relu"` and `residual` (fp16 [..., N], added last) fuse what follows the linear in
     a decoder block into the kernel's output stage (C ABI: bw_qmatmul_fused): the result equals
-    `torch.relu(linear) + residual` computed op by op in fp16.
+    `torch.relu(linear) + residual` computed op by op in fp16.  `activation="silu_mul"` is the
+    gated feed-forward as one GEMM: the packed weight holds (gate, up) row pairs (see
+    `interleave_gate_up`) and the result is `silu(gate) * up` of shape [..., N/2].
     """
     if bits not in (2, 4, 8):
         raise ValueError("Only 2, 4, or 8 bits are supported.")
@@ -65,22 +67,25 @@ def quantized_matmul_cuda(x, qweight, scale, zero_point, bias, bits, group_size,
     for name, t in (("qweight", qweight), ("scale", scale), ("zero_point", zero_point), ("bias", bias)):
         if t is not None and t.device != dev:
             raise RuntimeError(f"`{name}` is on {t.device} but x is on {dev}")
+    if activation not in (None, "relu", "silu_mul"):
+        raise ValueError("activation must be None, 'relu' or 'silu_mul'")
+    if activation == "silu_mul" and N % 4 != 0:
+        raise ValueError("'silu_mul' pairs adjacent weight rows (gate, up): out_features must be a multiple of 4")
+    N_out = N // 2 if activation == "silu_mul" else N
     if out is None:
-        out = torch.empty((M, N), dtype=out_dtype, device=dev)
+        out = torch.empty((M, N_out), dtype=out_dtype, device=dev)
     else:
-        if out.dtype != out_dtype or tuple(out.shape) != (M, N) or not out.is_contiguous() or out.device != dev:
-            raise ValueError("`out` must be a contiguous [M, N] tensor of out_dtype on x's device")
-    if activation not in (None, "relu"):
-        raise ValueError("activation must be None or 'relu'")
+        if out.dtype != out_dtype or tuple(out.shape) != (M, N_out) or not out.is_contiguous() or out.device != dev:
+            raise ValueError("`out` must be a contiguous [M, N] tensor of out_dtype on x's device ([M, N/2] for 'silu_mul')")
     ep = None
     if activation is not None or residual is not None:
         if residual is not None:
             _lib.require_cuda(residual, "residual")
-            if residual.dtype != torch.float16 or residual.numel() != M * N or residual.device != dev:
+            if residual.dtype != torch.float16 or residual.numel() != M * N_out or residual.device != dev:
                 raise ValueError("`residual` must be an fp16 tensor of the output's shape on x's device")
             residual = residual.contiguous()
-        ep = _lib.Epilogue(_lib.ACT_RELU if activation == "relu" else _lib.ACT_NONE,
-                           None if residual is None else residual.data_ptr())
+        act = {None: _lib.ACT_NONE, "relu": _lib.ACT_RELU, "silu_mul": _lib.ACT_SILU_MUL}[activation]
+        ep = _lib.Epilogue(act, None if residual is None else residual.data_ptr())
     L = _lib.lib()
     with torch.cuda.device(dev):
         ws_bytes = L.bw_qmatmul_workspace_bytes_for(M, N, K, bits, group_size, _lib.dtype_code(x2.dtype),
@@ -92,7 +97,16 @@ def quantized_matmul_cuda(x, qweight, scale, zero_point, bias, bits, group_size,
         tail = (_lib.ptr(ws), 0 if ws is None else ws.numel(), _lib.stream_ptr(dev))
         rc = L.bw_qmatmul(*args, *tail) if ep is None else L.bw_qmatmul_fused(*args, ep, *tail)
     _lib.check(rc)
-    return out.reshape(*x.shape[:-1], N)
+    return out.reshape(*x.shape[:-1], N_out)
+
+
+def interleave_gate_up(gate, up):
+    """Row-interleaves the tensors of a gate and an up projection (packed words, scales, zero points or
+    biases of equal shape): row 2i = gate row i, row 2i+1 = up row i -- the [2*ffn, K] layout that
+    `activation="silu_mul"` expects."""
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        raise ValueError("gate and up must have the same shape and dtype")
+    return torch.stack((gate, up), dim=1).reshape(2 * gate.shape[0], *gate.shape[1:]).contiguous()
 
 
 def quantized_matmul_grad_input(grad_output, qweight, scale, zero_point, bits, group_size):

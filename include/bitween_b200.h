@@ -179,12 +179,20 @@ BW_API int bw_qmatmul(const void *x, int x_dtype, int64_t M, int64_t N, int64_t 
  *   out = act( fp16(fp16(acc) + bias) ) + residual      (each step rounded to fp16 for BW_F16 out,
  *                                                         like the separate torch ops; fp32 math
  *                                                         with one final rounding otherwise)
- *   ep->activation  BW_ACT_NONE | BW_ACT_RELU
+ *   ep->activation  BW_ACT_NONE | BW_ACT_RELU | BW_ACT_SILU_MUL
  *   ep->residual    [M,N] fp16 or NULL; may alias `out`
  * ep == NULL is bw_qmatmul.
+ * BW_ACT_SILU_MUL is the gated feed-forward (Llama gate / up) as ONE [2*ffn, K] packed GEMM: row 2i
+ * of the packed weight (and of scale, zero_point, bias) is gate row i, row 2i+1 is up row i, and
+ *   out[m, i] = silu(lin[m, 2i]) * lin[m, 2i+1] (+ residual[m, i]),    out and residual are [M, N/2]
+ * with lin rounded as the plain call rounds it, silu evaluated in fp32, every step rounded to fp16
+ * for BW_F16 out (fp32 math with one final rounding otherwise).  N must be a multiple of 4.  Served
+ * by the decode kernel (M <= 32) and the tensor-core kernel; layouts neither can take return
+ * BW_ERR_UNSUPPORTED with nothing launched (the caller runs the plain call and its own elementwise op).
  */
 #define BW_ACT_NONE 0
 #define BW_ACT_RELU 1
+#define BW_ACT_SILU_MUL 2
 typedef struct {
     int activation;
     const void *residual;

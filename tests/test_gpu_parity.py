@@ -617,3 +617,43 @@ def test_host_buffer_call_equals_device_call(pinned, M, N, K, bits, g):
         torch.cuda.synchronize()
         assert torch.equal(hy, want2)
     assert _lib.lib().bw_device_status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 8, 16, 32, 64, 300])
+@pytest.mark.parametrize("bits,g,F,K,bias,res", [(4, 128, 1024, 2048, False, False), (8, 64, 256, 1024, True, True),
+                                                  (2, 64, 384, 512, True, False), (4, 128, 14336 // 8, 4096, False, True)])
+def test_fused_silu_mul_equals_the_separate_ops(M, bits, g, F, K, bias, res):
+    """The gated feed-forward as one [2F, K] GEMM with the SiLU * up epilogue against two plain calls
+    followed by torch's own silu and mul on fp16 tensors (and the residual add)."""
+    from bitween_b200.kernels.cuda_loader import interleave_gate_up
+    wg = torch.from_numpy(synth.normal(41, (F, K), 0.02)).to(DEV)
+    wu = torch.from_numpy(synth.normal(42, (F, K), 0.02)).to(DEV)
+    qg, sg, zg = _rtn_launch(wg, bits, g, torch.float16, torch.float16, True)
+    qu, su, zu = _rtn_launch(wu, bits, g, torch.float16, torch.float16, True)
+    bg = torch.from_numpy(synth.normal(43, (F,), 0.5)).to(DEV).half() if bias else None
+    bu = torch.from_numpy(synth.normal(44, (F,), 0.5)).to(DEV).half() if bias else None
+    x = torch.from_numpy(synth.normal(45, (M, K), 1.0)).to(DEV).to(torch.bfloat16)
+    r = torch.from_numpy(synth.normal(46, (M, F), 1.0)).to(DEV).half() if res else None
+    gate = quantized_matmul_cuda(x, qg, sg, zg, bg, bits, g)
+    up = quantized_matmul_cuda(x, qu, su, zu, bu, bits, g)
+    want = torch.nn.functional.silu(gate) * up
+    if res:
+        want = want + r
+    got = quantized_matmul_cuda(x, interleave_gate_up(qg, qu), interleave_gate_up(sg, su), interleave_gate_up(zg, zu),
+                                None if not bias else interleave_gate_up(bg, bu), bits, g, activation="silu_mul", residual=r)
+    assert tuple(got.shape) == (M, F) and got.dtype == torch.float16
+    assert _lib.last_qmatmul_kernel() == ("qmm_decode_kernel" if M <= 32 else "qmm_tc_kernel")
+    # the sums may be added in another order than in the two plain calls (other tiling of the rows), and
+    # expf may differ from torch's in the last place: a few fp16 ulps of the largest factor
+    a, b = as_f32(got), as_f32(want)
+    scale_ = np.maximum(np.abs(as_f32(up)), 1.0) * np.maximum(np.abs(as_f32(gate)), 1.0)
+    assert np.all(np.abs(a - b) <= 4 * 2.0 ** -10 * scale_ + (np.abs(as_f32(r)) * 2.0 ** -10 if res else 0.0))
+    # fp32 output: one rounding at the end
+    got32 = quantized_matmul_cuda(x, interleave_gate_up(qg, qu), interleave_gate_up(sg, su), interleave_gate_up(zg, zu),
+                                  None if not bias else interleave_gate_up(bg, bu), bits, g, activation="silu_mul",
+                                  out_dtype=torch.float32)
+    g32 = quantized_matmul_cuda(x, qg, sg, zg, bg, bits, g, out_dtype=torch.float32)
+    u32 = quantized_matmul_cuda(x, qu, su, zu, bu, bits, g, out_dtype=torch.float32)
+    want32 = torch.nn.functional.silu(g32) * u32
+    assert torch.allclose(got32, want32, rtol=1e-4, atol=1e-5 * float(want32.abs().max()) + 1e-7)
+    assert _lib.lib().bw_device_status() == 0
