@@ -632,6 +632,71 @@ def run_tp70b(args, torch, dist, rank, world, device):
         "allreduce_share": round(max(0.0, 1.0 - ms_no_ar / dec[best]), 3), "mode": best,
         "us_per_layer_by_mode": {k: round(v * 1e3 / layers_n, 1) for k, v in dec.items()},
         "kernel": _lib.last_qmatmul_kernel(), "allreduce_bytes": 64 * HIDDEN70 * 2}
+    # the same decode step with the launches a decoder really issues: q/k/v as one column-parallel GEMM,
+    # gate and up as one GEMM with the SiLU * up epilogue (interleaved row pairs), fp16 activations
+    # throughout (no per-call cast): 4 GEMMs and 2 all-reduces per layer instead of 7 and 2
+    from bitween_b200.kernels.cuda_loader import interleave_gate_up
+    fused_layers = []
+    for lay in layers:
+        d = {name: (n, k, q, s, z) for (name, mode, n, k, q, s, z) in lay}
+        cat = lambda i: torch.cat([d["q_proj"][i], d["k_proj"][i], d["v_proj"][i]], dim=0).contiguous()   # noqa: E731
+        fused_layers.append({
+            "qkv": (d["q_proj"][0] + d["k_proj"][0] + d["v_proj"][0], d["q_proj"][1], cat(2), cat(3), cat(4)),
+            "o": d["o_proj"],
+            "gate_up": (2 * d["gate_proj"][0], d["gate_proj"][1]) + tuple(interleave_gate_up(d["gate_proj"][i], d["up_proj"][i]) for i in (2, 3, 4)),
+            "down": d["down_proj"]})
+
+    def measure_fused(M, allreduce):
+        fl = fused_layers[0]
+        x_h = torch.randn(M, fl["qkv"][1], device=device, generator=gen).to(torch.float16)
+        x_o = torch.randn(M, fl["o"][1], device=device, generator=gen).to(torch.float16)
+        x_d = torch.randn(M, fl["down"][1], device=device, generator=gen).to(torch.float16)
+        y_qkv = torch.empty(M, fl["qkv"][0], device=device, dtype=torch.float16)
+        y_h = torch.empty(M, fl["o"][0], device=device, dtype=torch.float16)
+        y_act = torch.empty(M, fl["gate_up"][0] // 2, device=device, dtype=torch.float16)
+
+        def step():
+            for fl in fused_layers:
+                n, k, q, s, z = fl["qkv"]
+                qmm(x_h, q, s, z, None, bits, g, out=y_qkv)
+                n, k, q, s, z = fl["o"]
+                y = qmm(x_o, q, s, z, None, bits, g, out=y_h)
+                if allreduce and dist is not None:
+                    dist.all_reduce(y)
+                n, k, q, s, z = fl["gate_up"]
+                qmm(x_h, q, s, z, None, bits, g, out=y_act, activation="silu_mul")
+                n, k, q, s, z = fl["down"]
+                y = qmm(x_d, q, s, z, None, bits, g, out=y_h)
+                if allreduce and dist is not None:
+                    dist.all_reduce(y)
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        run_step = step
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            run_step = graph.replay
+        except Exception:   # noqa: BLE001  (a collective that cannot be captured: eager)
+            torch.cuda.synchronize()
+        for _ in range(3):
+            run_step()
+        if dist is not None:
+            dist.barrier()
+        total = 0.0
+        for _ in range(30):
+            flush.fill_(1)
+            total += time_region(torch, run_step)
+        return max_over_ranks(torch, dist, device, total / 30)
+
+    ms_f = measure_fused(64, True)
+    ms_f_no = measure_fused(64, False) if world > 1 else ms_f
+    res["decode64_fused"] = {
+        "us_per_layer": round(ms_f * 1e3 / layers_n, 1), "us_per_layer_without_allreduce": round(ms_f_no * 1e3 / layers_n, 1),
+        "GBps": round(algo[64] / (ms_f * 1e-3) / 1e9, 1), "launches_per_layer": 4,
+        "what": "q/k/v as one GEMM, gate/up as one GEMM with the SiLU * up epilogue, fp16 activations; same weights and all-reduces"}
+    del fused_layers
     # prefill 4096 tokens: plain, and with the row-parallel GEMMs chunked against their all-reduces
     pf = {"plain": measure(4096, True, False)}
     if world > 1:
