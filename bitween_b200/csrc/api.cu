@@ -57,6 +57,11 @@ int fake_quant(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int g
                const void *value, int value_dtype, float *dq, float *wq, cudaStream_t st);
 int fake_quant_backward(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int g, const float *scale, const float *zp,
                         const void *value, int value_dtype, const float *grad, float *gscale, float *gzp, cudaStream_t st);
+size_t peer_flag_bytes();
+size_t peer_state_bytes();
+int peer_device_status();
+int peer_allreduce_f16(const void *const *bufs, void *const *flags, int rank, int world, void *out, int64_t count, void *state,
+                       cudaStream_t st);
 int rtn_device_status();
 long long div_self_check(unsigned long long n, unsigned long long seed);
 int qmatmul_grad_input(const void *go, int dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
@@ -414,6 +419,47 @@ int bw_fake_quant_backward(const void *w, int w_dtype, int64_t N, int64_t K, int
                                grad_zero_point, (cudaStream_t)stream);
 }
 
+// ---- peer-memory all-reduce (row-parallel layers on one node) ----
+int bw_peer_alloc(size_t bytes, void **ptr, unsigned char *ipc_handle) {
+    if (!ptr || !ipc_handle || bytes == 0) return BW_ERR_NULL;
+    void *p = nullptr;
+    BW_CUDA_TRY(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        (void)cudaFree(p);
+        return record_cuda_error(e, "bw_peer_alloc");
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    memcpy(ipc_handle, &h, sizeof(h));
+    *ptr = p;
+    return BW_OK;
+}
+int bw_peer_open(const unsigned char *ipc_handle, void **ptr) {
+    if (!ptr || !ipc_handle) return BW_ERR_NULL;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, ipc_handle, sizeof(h));
+    BW_CUDA_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return BW_OK;
+}
+int bw_peer_close(void *ptr) {
+    if (!ptr) return BW_OK;
+    BW_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+    return BW_OK;
+}
+int bw_peer_free(void *ptr) {
+    if (!ptr) return BW_OK;
+    BW_CUDA_TRY(cudaFree(ptr));
+    return BW_OK;
+}
+size_t bw_peer_flag_bytes(void) { return peer_flag_bytes(); }
+size_t bw_peer_state_bytes(void) { return peer_state_bytes(); }
+int bw_peer_allreduce_f16(const void *const *bufs, void *const *flags, int rank, int world, void *out, int64_t count,
+                          void *state, void *stream) {
+    return peer_allreduce_f16(bufs, flags, rank, world, out, count, state, (cudaStream_t)stream);
+}
+
 const char *bw_status_string(int status) {
     switch (status) {
         case BW_OK: return "ok";
@@ -439,9 +485,9 @@ const char *bw_last_cuda_error(void) { return g_cuda_error; }
 
 int bw_device_status(void) {
     if (cudaDeviceSynchronize() != cudaSuccess) return record_cuda_error(cudaGetLastError(), "cudaDeviceSynchronize");
-    const int v = rtn_device_status(), t = tc_device_status(), d = decode_device_status();
-    if (v < 0 || t < 0 || d < 0) return BW_ERR_CUDA;
-    return (v || t || d) ? BW_ERR_TIMEOUT : BW_OK;
+    const int v = rtn_device_status(), t = tc_device_status(), d = decode_device_status(), pr = peer_device_status();
+    if (v < 0 || t < 0 || d < 0 || pr < 0) return BW_ERR_CUDA;
+    return (v || t || d || pr) ? BW_ERR_TIMEOUT : BW_OK;
 }
 int bw_version(void) { return 100; }
 const char *bw_last_qmatmul_kernel(void) { return g_last_kernel; }

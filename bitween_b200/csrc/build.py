@@ -16,7 +16,7 @@ OUT_DIR = os.path.join(PKG, "_C")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB = os.path.join(OUT_DIR, "libbitween_b200.so")
 
-SOURCES = ["api.cu", "rtn_quantize.cu", "dequantize.cu", "qmatmul_smallm.cu", "qmatmul_decode.cu", "qmatmul_tc.cu", "qmatmul_grad_input.cu", "fake_quant.cu"]
+SOURCES = ["api.cu", "rtn_quantize.cu", "dequantize.cu", "qmatmul_smallm.cu", "qmatmul_decode.cu", "qmatmul_tc.cu", "qmatmul_grad_input.cu", "fake_quant.cu", "peer_allreduce.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -60,6 +60,18 @@ def _declare(L):
     L.bw_rtn_batch_table_bytes.restype = sz
     L.bw_rtn_quantize_pack_batch.argtypes = [ctypes.POINTER(RtnJob), i32, i32, i32, i32, i32, i32, u32, vp, sz, vp]
     L.bw_rtn_quantize_pack_batch.restype = i32
+    L.bw_peer_alloc.argtypes = [sz, ctypes.POINTER(vp), ctypes.c_char_p]
+    L.bw_peer_alloc.restype = i32
+    L.bw_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+    L.bw_peer_open.restype = i32
+    L.bw_peer_close.argtypes = [vp]
+    L.bw_peer_close.restype = i32
+    L.bw_peer_free.argtypes = [vp]
+    L.bw_peer_free.restype = i32
+    L.bw_peer_flag_bytes.restype = sz
+    L.bw_peer_state_bytes.restype = sz
+    L.bw_peer_allreduce_f16.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i32, vp, i64, vp, vp]
+    L.bw_peer_allreduce_f16.restype = i32
     L.bw_fake_quant.argtypes = [vp, i32, i64, i64, i32, i32, vp, vp, vp, i32, vp, vp, vp]
     L.bw_fake_quant.restype = i32
     L.bw_fake_quant_backward.argtypes = [vp, i32, i64, i64, i32, i32, vp, vp, vp, i32, vp, vp, vp, vp]

@@ -105,19 +105,21 @@ class RowParallelQuantizedLinear(nn.Module):
     bandwidth, and stays one piece).  `reduce_dtype=torch.float32` makes every rank emit its
     partial sums unrounded and rounds once after the reduce -- the reference's single fp16
     rounding -- at twice the bytes on the wire; the default sums fp16 partials (one extra
-    rounding per rank, within the 1e-2 * RMS bar at 8 ranks)."""
+    rounding per rank, within the 1e-2 * RMS bar at 8 ranks).  `peer` (a `PeerAllReduce`) replaces
+    the NCCL all-reduce of outputs that fit its buffers by the peer-memory kernel."""
 
-    def __init__(self, shard: QuantizedLinear, group=None, overlap_chunks=1, reduce_dtype=None):
+    def __init__(self, shard: QuantizedLinear, group=None, overlap_chunks=1, reduce_dtype=None, peer=None):
         super().__init__()
         self.shard = shard
         self.group = group
         self.overlap_chunks = int(overlap_chunks)
         self.reduce_dtype = reduce_dtype
+        self.peer = peer          # a bitween_b200.peer.PeerAllReduce shared by the layers of a model, or None (NCCL)
         self._comm_stream = None
 
     @classmethod
-    def from_full(cls, layer, rank, world, group=None, overlap_chunks=1, reduce_dtype=None):
-        return cls(shard_quantized_linear(layer, "row", rank, world), group, overlap_chunks, reduce_dtype)
+    def from_full(cls, layer, rank, world, group=None, overlap_chunks=1, reduce_dtype=None, peer=None):
+        return cls(shard_quantized_linear(layer, "row", rank, world), group, overlap_chunks, reduce_dtype, peer)
 
     def _partial(self, x, out=None):
         s = self.shard
@@ -134,7 +136,15 @@ class RowParallelQuantizedLinear(nn.Module):
         x2 = x_shard.reshape(-1, s.in_features)
         M = x2.shape[0]
         chunks = min(self.overlap_chunks, M) if distributed and x2.is_cuda else 1
-        if chunks <= 1:
+        if (distributed and self.peer is not None and self.reduce_dtype is None and x2.is_cuda
+                and (M * s.out_features) % 8 == 0 and M * s.out_features <= self.peer.max_elems):
+            # the matmul writes its partial sums into peer-mapped memory and one kernel sums them over
+            # the ranks: no library collective (a decode step's all-reduce is bound by latency)
+            self._partial(x2, out=self.peer.partial(M, s.out_features))
+            y = torch.empty((M, s.out_features), dtype=torch.float16, device=x2.device)
+            self.peer.allreduce(y)
+            y = y.reshape(*x_shard.shape[:-1], s.out_features)
+        elif chunks <= 1:
             y = self._partial(x_shard)
             if distributed:
                 dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)

@@ -298,6 +298,34 @@ BW_API int bw_fake_quant_backward(const void *w, int w_dtype, int64_t N, int64_t
                            const void *value, int value_dtype, const float *grad_w_dq,
                            float *grad_scale, float *grad_zero_point, void *stream);
 
+/*
+ * All-reduce (sum) of the row-parallel layers' partial outputs over peer memory on one node,
+ * without NCCL.  No counterpart in the reference (it is single-GPU); it replaces the
+ * ncclAllReduce that follows o_proj / down_proj in the tensor-parallel layers of this library.
+ * Set-up (once): every rank allocates its partial-sum buffers and one flag array with
+ * bw_peer_alloc (cudaMalloc, zero-filled, plus a CUDA IPC handle of 64 bytes), the ranks exchange
+ * the handles by any means, and every rank maps the others' with bw_peer_open.  Per call: the
+ * rank's matmul writes its partial [count] fp16 values into its own buffer, then
+ * bw_peer_allreduce_f16 (same stream) waits -- bounded, BW_ERR_TIMEOUT through bw_device_status --
+ * until every rank's partial is complete, adds them in rank order in fp32 (the same bits on every
+ * rank) and writes the fp16 sums to `out` (local memory).
+ *   bufs, flags  host arrays of `world` device pointers: this process's mappings of rank r's
+ *                partial buffer and flag array (bw_peer_flag_bytes() bytes, zero at start)
+ *   state        bw_peer_state_bytes() bytes of local device memory, zero at start, one per flag array
+ *   count        multiple of 8; all ranks call with the same count, in the same order
+ * A buffer may be rewritten once ONE other call on the same flag array has been issued in
+ * between (callers alternate between two partial buffers).  world <= 8, one process per GPU.
+ * Plain peer loads and stores: no multicast object is created.
+ */
+BW_API int bw_peer_alloc(size_t bytes, void **ptr, unsigned char *ipc_handle_64);
+BW_API int bw_peer_open(const unsigned char *ipc_handle_64, void **ptr);
+BW_API int bw_peer_close(void *ptr);
+BW_API int bw_peer_free(void *ptr);
+BW_API size_t bw_peer_flag_bytes(void);
+BW_API size_t bw_peer_state_bytes(void);
+BW_API int bw_peer_allreduce_f16(const void *const *bufs, void *const *flags, int rank, int world, void *out,
+                          int64_t count, void *state, void *stream);
+
 /* Human-readable text for a bw_status. */
 BW_API const char *bw_status_string(int status);
 /* Text of the last CUDA error seen by this thread inside the library ("" if none). */
