@@ -565,7 +565,7 @@ def run_tp70b(args, torch, dist, rank, world, device):
     res = {"parallelism": f"tp{world}", "layers": layers_n, "scaling": "strong",
            "packed_MB_per_rank_per_layer": round(shard_bytes / 1e6, 1)}
 
-    def measure(M, allreduce, use_graph, chunks=1, steps=None):
+    def measure(M, allreduce, use_graph, chunks=1, steps=None, peer=None):
         ks = {k for (_, _, _, k, _, _, _) in layers[0]}
         ns = {n for (_, _, n, _, _, _, _) in layers[0]}
         xs = {k: torch.randn(M, k, device=device, generator=gen).to(torch.bfloat16) for k in ks}
@@ -588,6 +588,10 @@ def run_tp70b(args, torch, dist, rank, world, device):
                                 comm.wait_event(ev)
                                 dist.all_reduce(outs[n][lo:hi])
                         main.wait_stream(comm)
+                    elif mode == "row" and allreduce and peer is not None:
+                        # partial sums straight into peer-mapped memory, one kernel sums them over the ranks
+                        qmm(xs[k], q, s, z, None, bits, g, out=peer.partial(M, n))
+                        peer.allreduce(outs[n])
                     else:
                         y = qmm(xs[k], q, s, z, None, bits, g, out=outs[n])
                         if mode == "row" and allreduce and dist is not None:
@@ -646,7 +650,7 @@ def run_tp70b(args, torch, dist, rank, world, device):
             "gate_up": (2 * d["gate_proj"][0], d["gate_proj"][1]) + tuple(interleave_gate_up(d["gate_proj"][i], d["up_proj"][i]) for i in (2, 3, 4)),
             "down": d["down_proj"]})
 
-    def measure_fused(M, allreduce):
+    def measure_fused(M, allreduce, peer=None):
         fl = fused_layers[0]
         x_h = torch.randn(M, fl["qkv"][1], device=device, generator=gen).to(torch.float16)
         x_o = torch.randn(M, fl["o"][1], device=device, generator=gen).to(torch.float16)
@@ -660,15 +664,23 @@ def run_tp70b(args, torch, dist, rank, world, device):
                 n, k, q, s, z = fl["qkv"]
                 qmm(x_h, q, s, z, None, bits, g, out=y_qkv)
                 n, k, q, s, z = fl["o"]
-                y = qmm(x_o, q, s, z, None, bits, g, out=y_h)
-                if allreduce and dist is not None:
-                    dist.all_reduce(y)
+                if allreduce and peer is not None:
+                    qmm(x_o, q, s, z, None, bits, g, out=peer.partial(M, n))
+                    peer.allreduce(y_h)
+                else:
+                    y = qmm(x_o, q, s, z, None, bits, g, out=y_h)
+                    if allreduce and dist is not None:
+                        dist.all_reduce(y)
                 n, k, q, s, z = fl["gate_up"]
                 qmm(x_h, q, s, z, None, bits, g, out=y_act, activation="silu_mul")
                 n, k, q, s, z = fl["down"]
-                y = qmm(x_d, q, s, z, None, bits, g, out=y_h)
-                if allreduce and dist is not None:
-                    dist.all_reduce(y)
+                if allreduce and peer is not None:
+                    qmm(x_d, q, s, z, None, bits, g, out=peer.partial(M, n))
+                    peer.allreduce(y_h)
+                else:
+                    y = qmm(x_d, q, s, z, None, bits, g, out=y_h)
+                    if allreduce and dist is not None:
+                        dist.all_reduce(y)
         for _ in range(2):
             step()
         torch.cuda.synchronize()
@@ -690,12 +702,23 @@ def run_tp70b(args, torch, dist, rank, world, device):
             total += time_region(torch, run_step)
         return max_over_ranks(torch, dist, device, total / 30)
 
+    # the all-reduces through peer memory instead of NCCL (bitween_b200/peer.py), plain and fused launches
+    peer = None
+    if world > 1:
+        from bitween_b200.peer import PeerAllReduce
+        peer = PeerAllReduce(64 * HIDDEN70)
+        ms_p = measure(64, True, True, peer=peer)
+        if ms_p is not None:
+            res["decode64"]["us_per_layer_peer_allreduce"] = round(ms_p * 1e3 / layers_n, 1)
     ms_f = measure_fused(64, True)
     ms_f_no = measure_fused(64, False) if world > 1 else ms_f
     res["decode64_fused"] = {
         "us_per_layer": round(ms_f * 1e3 / layers_n, 1), "us_per_layer_without_allreduce": round(ms_f_no * 1e3 / layers_n, 1),
         "GBps": round(algo[64] / (ms_f * 1e-3) / 1e9, 1), "launches_per_layer": 4,
         "what": "q/k/v as one GEMM, gate/up as one GEMM with the SiLU * up epilogue, fp16 activations; same weights and all-reduces"}
+    if peer is not None:
+        res["decode64_fused"]["us_per_layer_peer_allreduce"] = round(measure_fused(64, True, peer=peer) * 1e3 / layers_n, 1)
+        peer.close()
     del fused_layers
     # prefill 4096 tokens: plain, and with the row-parallel GEMMs chunked against their all-reduces
     pf = {"plain": measure(4096, True, False)}
