@@ -706,10 +706,14 @@ def run_tp70b(args, torch, dist, rank, world, device):
     peer = None
     if world > 1:
         from bitween_b200.peer import PeerAllReduce
-        peer = PeerAllReduce(64 * HIDDEN70)
-        ms_p = measure(64, True, True, peer=peer)
-        if ms_p is not None:
-            res["decode64"]["us_per_layer_peer_allreduce"] = round(ms_p * 1e3 / layers_n, 1)
+        try:
+            peer = PeerAllReduce(64 * HIDDEN70)          # raises on every rank if any rank cannot map its peers
+        except RuntimeError as e:
+            res["decode64"]["peer_allreduce"] = f"unavailable: {e}"
+        if peer is not None:
+            ms_p = measure(64, True, True, peer=peer)
+            if ms_p is not None:
+                res["decode64"]["us_per_layer_peer_allreduce"] = round(ms_p * 1e3 / layers_n, 1)
     ms_f = measure_fused(64, True)
     ms_f_no = measure_fused(64, False) if world > 1 else ms_f
     res["decode64_fused"] = {

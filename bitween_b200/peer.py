@@ -46,26 +46,48 @@ class PeerAllReduce:
         self._local, self._opened = [], []
         nbytes = self.max_elems * 2
         with torch.cuda.device(self.device):
-            mine = [self._alloc(nbytes), self._alloc(nbytes), self._alloc(L.bw_peer_flag_bytes())]
+            # Every step that can fail locally is followed by an agreement over the group, so that a
+            # failure on one rank raises on all of them instead of leaving the others in a collective.
+            mine, err = [], None
+            try:
+                mine = [self._alloc(nbytes), self._alloc(nbytes), self._alloc(L.bw_peer_flag_bytes())]
+            except Exception as e:   # noqa: BLE001
+                err = e
+            self._agree(err, "allocating the peer buffers")
             gathered = [None] * self.world
             dist.all_gather_object(gathered, [h for (_, h) in mine], group=group)
             # ptrs[i][r]: this process's mapping of rank r's allocation i (0, 1: partial buffers, 2: flags)
             self._ptrs = [[None] * self.world for _ in range(3)]
-            for r in range(self.world):
-                for i in range(3):
-                    if r == self.rank:
-                        self._ptrs[i][r] = mine[i][0]
-                    else:
-                        p = ctypes.c_void_p()
-                        _lib.check(L.bw_peer_open(gathered[r][i], ctypes.byref(p)))
-                        self._opened.append(p.value)
-                        self._ptrs[i][r] = p.value
+            try:
+                for r in range(self.world):
+                    for i in range(3):
+                        if r == self.rank:
+                            self._ptrs[i][r] = mine[i][0]
+                        else:
+                            p = ctypes.c_void_p()
+                            _lib.check(L.bw_peer_open(gathered[r][i], ctypes.byref(p)))
+                            self._opened.append(p.value)
+                            self._ptrs[i][r] = p.value
+            except Exception as e:   # noqa: BLE001
+                err = e
+            self._agree(err, "mapping the peers' buffers (CUDA IPC)")
             self._state = torch.zeros(L.bw_peer_state_bytes(), dtype=torch.uint8, device=self.device)
         self._views = [torch.as_tensor(_RawCudaBuffer(mine[i][0], nbytes), device=self.device).view(torch.float16) for i in (0, 1)]
         self._arrays = [(ctypes.c_void_p * self.world)(*self._ptrs[i]) for i in range(3)]
         self._next = 0
         self._pending = None
         dist.barrier(group=group)          # every rank has mapped everything before the first call
+
+    def _agree(self, err, what):
+        ok = torch.tensor([0 if err is not None else 1], device=self.device, dtype=torch.int32)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) == 0:
+            for p in self._opened:
+                self._L.bw_peer_close(p)
+            for p in self._local:
+                self._L.bw_peer_free(p)
+            self._opened, self._local = [], []
+            raise RuntimeError(f"PeerAllReduce: {what} failed on " + ("this rank: " + repr(err) if err is not None else "another rank"))
 
     def _alloc(self, nbytes):
         p = ctypes.c_void_p()
