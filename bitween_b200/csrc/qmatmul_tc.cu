@@ -668,14 +668,14 @@ int launch_tc(const CUtensorMap &xmap, const CUtensorMap &wmap, const CUtensorMa
     const int64_t tiles = ((p.N + TC_BM - 1) / TC_BM) * ((p.M + p.bn - 1) / p.bn);
     int splits = 1;
     if (g_tc_splits > 0) splits = g_tc_splits;
-    else if (p.bn <= 128 && tiles < 148) {
+    else if (tiles < 148) {
         splits = (int)(148 / tiles);
         if (splits > 8) splits = 8;
         if (splits > p.k_stages / 4) splits = p.k_stages / 4;
         if (splits < 1) splits = 1;
     }
     const size_t red_bytes = (size_t)(p.bn < 32 ? 32 : p.bn) * TC_BM * 4;
-    if (splits > 8 || p.bn > 128 || red_bytes > (size_t)nsx * x_stage + (size_t)nsw * w_stage) splits = 1;
+    if (splits > 8 || red_bytes > (size_t)nsx * x_stage + (size_t)nsw * w_stage) splits = 1;
     if (splits > 1) p.tma_store = 0;   // split-K tiles are summed by the cluster and stored from registers
     p.splits = splits;
     p.kper = (p.k_stages + splits - 1) / splits;
