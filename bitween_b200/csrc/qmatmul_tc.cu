@@ -200,6 +200,7 @@ struct TcParams {
     int tiles;          // output tiles: n_tiles x token tiles
     int persistent;     // 1: grid.x CTAs walk the tile list (tile = blockIdx.x, += gridDim.x); 0: one tile per CTA
     int tma_store;      // 1: output blocks leave through a shared-memory staging tile and TMA stores
+    int pdl;            // 1: launched with programmatic stream serialisation behind the kernel that casts the activations
     int x_is_bf16;      // always 0: kind::f16 MMAs take both operands in one 16-bit format
     Epilogue ep;        // activation / residual add on the way out
 };
@@ -314,6 +315,10 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
             unsigned phx = 0, phw = 0, idle = 0;
             int gx = 0;                             // activation stages requested so far, over all tiles
             bool alive = true;
+            // Launched behind the activations' cast with programmatic stream serialisation: set-up and the
+            // packed-word requests (weights never depend on the preceding kernel) run beside it, the
+            // first activation request waits for it.
+            bool waited = p.pdl == 0;
             int t = first_tile;
             do {   // (one trip, known at compile time, when not persistent)
                 const int n0 = (t % p.n_tiles) * TC_BM, m0 = (t / p.n_tiles) * bn;
@@ -323,10 +328,8 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
                     if (iw < nslots) {
                         const int s = sw;
                         if (mbar_try_wait(&w_empty[s], phw ^ 1u)) {
-                            {
                             mbar_expect_tx(&w_full[s], (unsigned)W_STAGE_BYTES);
                             tma_load_2d(w_tiles + (size_t)s * W_STAGE_BYTES, &w_map, (kt0 + iw * SG::SPS) * SG::WPS, n0, &w_full[s]);
-                            }
                             ++iw;
                             if (++sw == NSW) { sw = 0; phw ^= 1u; }
                             progressed = true;
@@ -338,10 +341,12 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
                         // that is the commit that also frees the A stage of that k-stage (one per stage)
                         const int jf = gx - NSX;
                         if (jf < 0 || mbar_try_wait(&a_empty[jf % TC_STAGES], (unsigned)(jf / TC_STAGES) & 1u)) {
-                            {
+                            if (!waited) {
+                                asm volatile("griddepcontrol.wait;" ::: "memory");
+                                waited = true;
+                            }
                             mbar_expect_tx(&x_full[s], (unsigned)bn * 128u);
                             tma_load_2d(x_tiles + (size_t)s * bn * 128, &x_map, (kt0 + ix) * TC_BK, m0, &x_full[s]);
-                            }
                             ++ix;
                             ++gx;
                             if (++sx == NSX) { sx = 0; phx ^= 1u; }
@@ -618,6 +623,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
 // Activations that are not fp16 are cast once (bitween/modules.py:74) into caller scratch.
 template <typename XT>
 __global__ void __launch_bounds__(256) cast_to_f16_kernel(const XT *__restrict__ x, __half *__restrict__ y, int64_t n) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // the GEMM behind it may start its set-up
     const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (i + 8 <= n) {
         alignas(16) __half h[8];
@@ -712,13 +718,22 @@ int launch_tc(const CUtensorMap &xmap, const CUtensorMap &wmap, const CUtensorMa
     cfg.blockDim = dim3(TC_THREADS, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = (unsigned)splits;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (splits > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = (unsigned)splits;
+        ++na;
+    }
+    if (p.pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = splits > 1 ? 1 : 0;
+    cfg.numAttrs = na;
     if (p.persistent && p.tma_store) BW_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_tc_kernel<BITS, true, true>, xmap, wmap, omap, p));
     else if (p.persistent) BW_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_tc_kernel<BITS, true, false>, xmap, wmap, omap, p));
     else if (p.tma_store) BW_CUDA_TRY(cudaLaunchKernelEx(&cfg, qmm_tc_kernel<BITS, false, true>, xmap, wmap, omap, p));
@@ -790,6 +805,7 @@ int qmatmul_tc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
     p.k_stages = (int)((K + TC_BK - 1) / TC_BK);
     p.bn = M > 128 ? 256 : (M > 64 ? 128 : (M > 32 ? 64 : (M > 16 ? 32 : 16)));
     p.x_is_bf16 = 0;
+    p.pdl = direct ? 0 : 1;      // the cast kernel precedes this launch in the stream
     p.ep = current_epilogue();
 
     CUtensorMap map;
