@@ -13,13 +13,13 @@
 // of a k-stage into 32 columns of that lane with tcgen05.st; the MMAs read A from tensor
 // memory and only the activations (B) from shared memory.
 //
-// Warp roles in a CTA of 576 threads (one output tile of 128 weight rows x BN tokens, BN from
+// Warp roles in a CTA of 608 threads (one output tile of 128 weight rows x BN tokens, BN from
 // 16 to 256 by token count):
-//   warp 0       TMA producer (one lane): cp.async.bulk.tensor loads, without multicast, of
-//                the [BN tokens x 64 k] fp16 activation tile (128-byte swizzle) of each k-stage
-//                and of packed-word slots [128 rows x 128 bytes] (2, 4 or 8 k-stages, 128-byte
-//                swizzle: whole 128-byte row segments keep the weight stream's DRAM accesses
-//                efficient), in two independent shared-memory rings
+//   warp 0       TMA producer (one lane) of the [BN tokens x 64 k] fp16 activation tile (128-byte
+//                swizzle) of each k-stage: cp.async.bulk.tensor loads, without multicast
+//   warp 18      TMA producer (one lane) of the packed-word slots [128 rows x 128 bytes] (2, 4 or
+//                8 k-stages, 128-byte swizzle: whole 128-byte row segments keep the weight
+//                stream's DRAM accesses efficient); the two rings are independent
 //   warp 1       allocates tensor memory (accumulator + eight A stages); the whole warp runs the
 //                issue loop and one elected lane issues
 //                tcgen05.mma (kind::f16, A in TMEM, M=128, N=BN, K=16, four per stage) and one
@@ -50,7 +50,8 @@ constexpr int TC_BM = 128;        // weight rows per tile (MMA M)
 constexpr int TC_BK = 64;         // k per stage: 64 fp16 = one 128-byte swizzle row
 constexpr int TC_STAGES = 8;       // A-operand stages in tensor memory (8 x 32 columns next to a 256-column accumulator)
 constexpr int TC_DQ_GROUPS = 4;   // dequantization warp groups (4 warps each) taking alternate stages
-constexpr int TC_THREADS = 64 + TC_DQ_GROUPS * 128;
+constexpr int TC_THREADS = 64 + TC_DQ_GROUPS * 128 + 32;
+constexpr int TC_WPROD_WARP = TC_THREADS / 32 - 1;   // the last warp: producer of the packed-word ring
 static_assert(TC_STAGES % TC_DQ_GROUPS == 0, "each dequantization group owns whole A stages (phase parity)");
 constexpr unsigned TC_WAIT_LIMIT = 1u << 22;   // polls of >= 20 ns each: gives up after ~0.1-1 s
 
@@ -307,56 +308,46 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ---- TMA producer: two independent rings, activations and packed weight words ----
-        // (the small packed-word stages are freed by the dequantization warps as soon as they
-        // have been read into registers, so this ring runs far ahead of the tensor core)
+        // ---- TMA producer of the activation tiles (one thread) ----
+        // (Each ring has its own producer thread: one thread serving both spent ~250 cycles per k-stage
+        // on mbarrier round trips and TMA issue, which bounded a k-stage of small token tiles.)
         if (lane == 0) {
-            int sx = 0, sw = 0;                     // ring slots and phases advance without divisions
-            unsigned phx = 0, phw = 0, idle = 0;
-            int gx = 0;                             // activation stages requested so far, over all tiles
+            int sx = 0, gx = 0;                     // ring slot; activation stages requested so far, over all tiles
             bool alive = true;
             // Launched behind the activations' cast with programmatic stream serialisation: set-up and the
             // packed-word requests (weights never depend on the preceding kernel) run beside it, the
             // first activation request waits for it.
-            bool waited = p.pdl == 0;
+            if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
             int t = first_tile;
             do {   // (one trip, known at compile time, when not persistent)
-                const int n0 = (t % p.n_tiles) * TC_BM, m0 = (t / p.n_tiles) * bn;
-                int ix = 0, iw = 0;
-                while (ix < nk || iw < nslots) {
-                    bool progressed = false;
-                    if (iw < nslots) {
-                        const int s = sw;
-                        if (mbar_try_wait(&w_empty[s], phw ^ 1u)) {
-                            mbar_expect_tx(&w_full[s], (unsigned)W_STAGE_BYTES);
-                            tma_load_2d(w_tiles + (size_t)s * W_STAGE_BYTES, &w_map, (kt0 + iw * SG::SPS) * SG::WPS, n0, &w_full[s]);
-                            ++iw;
-                            if (++sw == NSW) { sw = 0; phw ^= 1u; }
-                            progressed = true;
-                        }
-                    }
-                    if (ix < nk) {
-                        const int s = sx;
-                        // the slot is free once the MMAs of the stage NSX positions back have completed:
-                        // that is the commit that also frees the A stage of that k-stage (one per stage)
-                        const int jf = gx - NSX;
-                        if (jf < 0 || mbar_try_wait(&a_empty[jf % TC_STAGES], (unsigned)(jf / TC_STAGES) & 1u)) {
-                            if (!waited) {
-                                asm volatile("griddepcontrol.wait;" ::: "memory");
-                                waited = true;
-                            }
-                            mbar_expect_tx(&x_full[s], (unsigned)bn * 128u);
-                            tma_load_2d(x_tiles + (size_t)s * bn * 128, &x_map, (kt0 + ix) * TC_BK, m0, &x_full[s]);
-                            ++ix;
-                            ++gx;
-                            if (++sx == NSX) { sx = 0; phx ^= 1u; }
-                            progressed = true;
-                        }
-                    }
-                    if (progressed) { idle = 0; continue; }
-                    if (*abort_flag) { alive = false; break; }
-                    // (no sleep between polls: this single thread is what keeps both rings full)
-                    if (++idle > 64u * TC_WAIT_LIMIT) { *abort_flag = 1; atomicExch(&g_tc_status, 1); alive = false; break; }
+                const int m0 = (t / p.n_tiles) * bn;
+                for (int ix = 0; ix < nk && alive; ++ix, ++gx) {
+                    // the slot is free once the MMAs of the stage NSX positions back have completed:
+                    // that is the commit that also frees the A stage of that k-stage (one per stage)
+                    const int jf = gx - NSX;
+                    if (jf >= 0 && !mbar_wait(&a_empty[jf % TC_STAGES], (unsigned)(jf / TC_STAGES) & 1u, abort_flag, 1)) { alive = false; break; }
+                    mbar_expect_tx(&x_full[sx], (unsigned)bn * 128u);
+                    tma_load_2d(x_tiles + (size_t)sx * bn * 128, &x_map, (kt0 + ix) * TC_BK, m0, &x_full[sx]);
+                    if (++sx == NSX) sx = 0;
+                }
+            } while (PERSIST && alive && (t += tile_step) < p.tiles);
+        }
+    } else if (warp == TC_WPROD_WARP) {
+        // ---- TMA producer of the packed-word slots (one thread) ----
+        // (the slots are freed by the dequantization warps as soon as they have been read into
+        // registers, so this ring runs far ahead of the tensor core)
+        if (lane == 0) {
+            int sw = 0;
+            unsigned phw = 0;
+            bool alive = true;
+            int t = first_tile;
+            do {
+                const int n0 = (t % p.n_tiles) * TC_BM;
+                for (int iw = 0; iw < nslots && alive; ++iw) {
+                    if (!mbar_wait(&w_empty[sw], phw ^ 1u, abort_flag, 1)) { alive = false; break; }
+                    mbar_expect_tx(&w_full[sw], (unsigned)W_STAGE_BYTES);
+                    tma_load_2d(w_tiles + (size_t)sw * W_STAGE_BYTES, &w_map, (kt0 + iw * SG::SPS) * SG::WPS, n0, &w_full[sw]);
+                    if (++sw == NSW) { sw = 0; phw ^= 1u; }
                 }
             } while (PERSIST && alive && (t += tile_step) < p.tiles);
         }
@@ -588,7 +579,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__
         float *red = reinterpret_cast<float *>(x_tiles);
         const int n0 = blockIdx.x * TC_BM, m0 = blockIdx.y * bn;     // split-K launches are never persistent
         cluster.sync();
-        if (warp >= 2 && *abort_flag == 0) {
+        if (warp >= 2 && warp < TC_WPROD_WARP && *abort_flag == 0) {
             const int rank = (int)cluster.block_rank(), nranks = (int)cluster.num_blocks();
             const int cols = bn < 32 ? 32 : bn;
             const int per_rank = (cols + nranks - 1) / nranks;
