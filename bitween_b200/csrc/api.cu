@@ -60,8 +60,8 @@ int fake_quant_backward(const void *w, int w_dtype, int64_t N, int64_t K, int bi
 size_t peer_flag_bytes();
 size_t peer_state_bytes();
 int peer_device_status();
-int peer_allreduce_f16(const void *const *bufs, void *const *flags, int rank, int world, void *out, int64_t count, void *state,
-                       cudaStream_t st);
+int peer_allreduce_f16(const void *const *bufs, void *const *res, void *const *flags, int rank, int world, void *out, int64_t count,
+                       void *state, cudaStream_t st);
 int rtn_device_status();
 long long div_self_check(unsigned long long n, unsigned long long seed);
 int qmatmul_grad_input(const void *go, int dtype, int64_t M, int64_t N, int64_t K, const int32_t *q,
@@ -457,7 +457,12 @@ size_t bw_peer_flag_bytes(void) { return peer_flag_bytes(); }
 size_t bw_peer_state_bytes(void) { return peer_state_bytes(); }
 int bw_peer_allreduce_f16(const void *const *bufs, void *const *flags, int rank, int world, void *out, int64_t count,
                           void *state, void *stream) {
-    return peer_allreduce_f16(bufs, flags, rank, world, out, count, state, (cudaStream_t)stream);
+    return peer_allreduce_f16(bufs, nullptr, flags, rank, world, out, count, state, (cudaStream_t)stream);
+}
+int bw_peer_allreduce2_f16(const void *const *bufs, void *const *results, void *const *flags, int rank, int world, void *out,
+                           int64_t count, void *state, void *stream) {
+    if (!results) return BW_ERR_NULL;
+    return peer_allreduce_f16(bufs, results, flags, rank, world, out, count, state, (cudaStream_t)stream);
 }
 
 const char *bw_status_string(int status) {

@@ -72,6 +72,8 @@ def _declare(L):
     L.bw_peer_state_bytes.restype = sz
     L.bw_peer_allreduce_f16.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i32, vp, i64, vp, vp]
     L.bw_peer_allreduce_f16.restype = i32
+    L.bw_peer_allreduce2_f16.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i32, vp, i64, vp, vp]
+    L.bw_peer_allreduce2_f16.restype = i32
     L.bw_fake_quant.argtypes = [vp, i32, i64, i64, i32, i32, vp, vp, vp, i32, vp, vp, vp]
     L.bw_fake_quant.restype = i32
     L.bw_fake_quant_backward.argtypes = [vp, i32, i64, i64, i32, i32, vp, vp, vp, i32, vp, vp, vp, vp]

@@ -32,7 +32,7 @@ class PeerAllReduce:
     fp16 [M, N] tensor for the matmul to write into; `allreduce(out)` then sums it over the ranks
     into `out`.  Calls must be issued in the same order on every rank, on one stream per rank."""
 
-    def __init__(self, max_elems, group=None, device=None):
+    def __init__(self, max_elems, group=None, device=None, algo="auto"):
         if not dist.is_initialized():
             raise RuntimeError("PeerAllReduce needs an initialised process group")
         self.group = group
@@ -41,6 +41,13 @@ class PeerAllReduce:
             raise ValueError("PeerAllReduce serves at most 8 ranks (one node)")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.max_elems = (int(max_elems) + 7) // 8 * 8
+        if algo not in ("auto", "one_shot", "two_shot"):
+            raise ValueError("algo must be 'auto', 'one_shot' or 'two_shot'")
+        # one-shot: every rank reads every partial (world-1 times the data per rank, one barrier);
+        # two-shot: reduce one slice each, publish, collect (2*(world-1)/world of the data, two barriers).
+        # At the 1 MiB of a decode step the second barrier costs more than the bytes it saves (8 GPUs:
+        # 21 us one-shot, 32 us two-shot, 34 us NCCL), so "auto" is one-shot; two-shot is for larger messages.
+        self.two_shot = algo == "two_shot"
         L = _lib.lib()
         self._L = L
         self._local, self._opened = [], []
@@ -50,17 +57,20 @@ class PeerAllReduce:
             # failure on one rank raises on all of them instead of leaving the others in a collective.
             mine, err = [], None
             try:
-                mine = [self._alloc(nbytes), self._alloc(nbytes), self._alloc(L.bw_peer_flag_bytes())]
+                slice_bytes = ((self.max_elems // 8 + self.world - 1) // self.world) * 16
+                mine = [self._alloc(nbytes), self._alloc(nbytes), self._alloc(L.bw_peer_flag_bytes()),
+                        self._alloc(slice_bytes), self._alloc(slice_bytes)]
             except Exception as e:   # noqa: BLE001
                 err = e
             self._agree(err, "allocating the peer buffers")
             gathered = [None] * self.world
             dist.all_gather_object(gathered, [h for (_, h) in mine], group=group)
-            # ptrs[i][r]: this process's mapping of rank r's allocation i (0, 1: partial buffers, 2: flags)
-            self._ptrs = [[None] * self.world for _ in range(3)]
+            # ptrs[i][r]: this process's mapping of rank r's allocation i (0, 1: partial buffers, 2: flags,
+            # 3, 4: reduced slices of the two-shot form)
+            self._ptrs = [[None] * self.world for _ in range(5)]
             try:
                 for r in range(self.world):
-                    for i in range(3):
+                    for i in range(5):
                         if r == self.rank:
                             self._ptrs[i][r] = mine[i][0]
                         else:
@@ -73,7 +83,7 @@ class PeerAllReduce:
             self._agree(err, "mapping the peers' buffers (CUDA IPC)")
             self._state = torch.zeros(L.bw_peer_state_bytes(), dtype=torch.uint8, device=self.device)
         self._views = [torch.as_tensor(_RawCudaBuffer(mine[i][0], nbytes), device=self.device).view(torch.float16) for i in (0, 1)]
-        self._arrays = [(ctypes.c_void_p * self.world)(*self._ptrs[i]) for i in range(3)]
+        self._arrays = [(ctypes.c_void_p * self.world)(*self._ptrs[i]) for i in range(5)]
         self._next = 0
         self._pending = None
         dist.barrier(group=group)          # every rank has mapped everything before the first call
@@ -111,8 +121,13 @@ class PeerAllReduce:
         if out.dtype != torch.float16 or not out.is_contiguous() or out.numel() != count or out.device != self.device:
             raise ValueError("`out` must be a contiguous fp16 tensor of the partial's size on this rank's device")
         with torch.cuda.device(self.device):
-            rc = self._L.bw_peer_allreduce_f16(self._arrays[which], self._arrays[2], self.rank, self.world, _lib.ptr(out),
-                                               count, _lib.ptr(self._state), _lib.stream_ptr(self.device))
+            if self.two_shot:
+                rc = self._L.bw_peer_allreduce2_f16(self._arrays[which], self._arrays[3 + which], self._arrays[2], self.rank,
+                                                    self.world, _lib.ptr(out), count, _lib.ptr(self._state),
+                                                    _lib.stream_ptr(self.device))
+            else:
+                rc = self._L.bw_peer_allreduce_f16(self._arrays[which], self._arrays[2], self.rank, self.world, _lib.ptr(out),
+                                                   count, _lib.ptr(self._state), _lib.stream_ptr(self.device))
         _lib.check(rc)
         self._pending = None
         self._next ^= 1

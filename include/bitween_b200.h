@@ -325,6 +325,15 @@ BW_API size_t bw_peer_flag_bytes(void);
 BW_API size_t bw_peer_state_bytes(void);
 BW_API int bw_peer_allreduce_f16(const void *const *bufs, void *const *flags, int rank, int world, void *out,
                           int64_t count, void *state, void *stream);
+/*
+ * Two-shot form of the same all-reduce for many ranks: every rank sums one slice of the data and
+ * publishes it in its result buffer (`results`: mappings of every rank's, ceil(count/world) values
+ * rounded up to 8, alternated like the partial buffers), a second barrier, then every rank collects
+ * the slices.  Per rank 2*(world-1)/world of the data crosses NVLink instead of (world-1) times
+ * all of it.  Same sums, same bits as the one-shot form.
+ */
+BW_API int bw_peer_allreduce2_f16(const void *const *bufs, void *const *results, void *const *flags, int rank,
+                           int world, void *out, int64_t count, void *state, void *stream);
 
 /* Human-readable text for a bw_status. */
 BW_API const char *bw_status_string(int status);

@@ -20,7 +20,8 @@ def main():
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
-    peer = PeerAllReduce(64 * 8192)
+    algo = os.environ.get("BW_PEER_ALGO", "auto")
+    peer = PeerAllReduce(64 * 8192, algo=algo)
     gen = torch.Generator(device=dev).manual_seed(100 + rank)
 
     def reference(part):
@@ -100,9 +101,10 @@ def main():
     rms = float(y_nccl.float().pow(2).mean().sqrt())
     assert err <= 4 * 2.0 ** -10 * max(rms, float(y_nccl.float().abs().max())), (err, rms)   # fp16 sums in another order
     assert _lib.lib().bw_device_status() == 0
+    two_shot = peer.two_shot
     peer.close()
     if rank == 0:
-        print(f"peer all-reduce ok: world={world} 1 MiB all-reduce {us_peer:.1f} us (peer kernel) vs {us_nccl:.1f} us (NCCL)", flush=True)
+        print(f"peer all-reduce ok: world={world} two_shot={two_shot} 1 MiB all-reduce {us_peer:.1f} us (peer kernel) vs {us_nccl:.1f} us (NCCL)", flush=True)
     dist.barrier()
     dist.destroy_process_group()
 
