@@ -141,11 +141,7 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_allreduce2_kernel(const Pee
     bool ok = block_barrier(a, rank, world, 0, epoch, &timed_out);
     if (ok) {
         const int64_t lo = rank * per, n = min(per, chunks - lo);
-        for (int64_t j = first; j < n; j += stride) {
-            uint4 v[PEER_MAX_RANKS];
-#pragma unroll
-            for (int r = 0; r < PEER_MAX_RANKS; ++r)
-                if (r < world) v[r] = __ldcg(reinterpret_cast<const uint4 *>(a.buf[r]) + lo + j);
+        auto reduce_chunk = [&](const uint4 (&v)[PEER_MAX_RANKS]) {
             float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int r = 0; r < PEER_MAX_RANKS; ++r) {
@@ -163,7 +159,31 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_allreduce2_kernel(const Pee
             __half2 *oh = reinterpret_cast<__half2 *>(&o);
 #pragma unroll
             for (int q = 0; q < 4; ++q) oh[q] = __floats2half2_rn(acc[2 * q], acc[2 * q + 1]);
-            reinterpret_cast<uint4 *>(a.res[rank])[j] = o;       // my slice, where the peers will fetch it
+            return o;
+        };
+        int64_t j = first;
+        // two chunks per thread in flight (large messages are bound by the bytes in flight over NVLink)
+        for (; j + stride < n; j += 2 * stride) {
+            uint4 v0[PEER_MAX_RANKS], v1[PEER_MAX_RANKS];
+#pragma unroll
+            for (int r = 0; r < PEER_MAX_RANKS; ++r)
+                if (r < world) {
+                    v0[r] = __ldcg(reinterpret_cast<const uint4 *>(a.buf[r]) + lo + j);
+                    v1[r] = __ldcg(reinterpret_cast<const uint4 *>(a.buf[r]) + lo + j + stride);
+                }
+            const uint4 o0 = reduce_chunk(v0), o1 = reduce_chunk(v1);
+            reinterpret_cast<uint4 *>(a.res[rank])[j] = o0;          // my slice, where the peers will fetch it
+            reinterpret_cast<uint4 *>(a.res[rank])[j + stride] = o1;
+            reinterpret_cast<uint4 *>(out)[lo + j] = o0;
+            reinterpret_cast<uint4 *>(out)[lo + j + stride] = o1;
+        }
+        for (; j < n; j += stride) {
+            uint4 v[PEER_MAX_RANKS];
+#pragma unroll
+            for (int r = 0; r < PEER_MAX_RANKS; ++r)
+                if (r < world) v[r] = __ldcg(reinterpret_cast<const uint4 *>(a.buf[r]) + lo + j);
+            const uint4 o = reduce_chunk(v);
+            reinterpret_cast<uint4 *>(a.res[rank])[j] = o;
             reinterpret_cast<uint4 *>(out)[lo + j] = o;
         }
         ok = block_barrier(a, rank, world, 1, epoch, &timed_out);
@@ -172,7 +192,15 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_allreduce2_kernel(const Pee
         for (int p = 0; p < world; ++p) {
             if (p == rank) continue;
             const int64_t lo = p * per, n = min(per, chunks - lo);
-            for (int64_t j = first; j < n; j += stride)
+            int64_t j = first;
+            for (; j + 3 * stride < n; j += 4 * stride) {            // four loads in flight per thread
+                uint4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u] = __ldcg(reinterpret_cast<const uint4 *>(a.res[p]) + j + u * stride);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) reinterpret_cast<uint4 *>(out)[lo + j + u * stride] = v[u];
+            }
+            for (; j < n; j += stride)
                 reinterpret_cast<uint4 *>(out)[lo + j] = __ldcg(reinterpret_cast<const uint4 *>(a.res[p]) + j);
         }
     }

@@ -46,7 +46,8 @@ class PeerAllReduce:
         # one-shot: every rank reads every partial (world-1 times the data per rank, one barrier);
         # two-shot: reduce one slice each, publish, collect (2*(world-1)/world of the data, two barriers).
         # At the 1 MiB of a decode step the second barrier costs more than the bytes it saves (8 GPUs:
-        # 21 us one-shot, 32 us two-shot, 34 us NCCL), so "auto" is one-shot; two-shot is for larger messages.
+        # 21 us one-shot, 32 us two-shot, 34 us NCCL), so "auto" is one-shot up to 4 MiB and two-shot beyond.
+        self.algo = algo
         self.two_shot = algo == "two_shot"
         L = _lib.lib()
         self._L = L
@@ -121,7 +122,7 @@ class PeerAllReduce:
         if out.dtype != torch.float16 or not out.is_contiguous() or out.numel() != count or out.device != self.device:
             raise ValueError("`out` must be a contiguous fp16 tensor of the partial's size on this rank's device")
         with torch.cuda.device(self.device):
-            if self.two_shot:
+            if self.two_shot or (self.algo == "auto" and count * 2 > (4 << 20) and self.world > 2):
                 rc = self._L.bw_peer_allreduce2_f16(self._arrays[which], self._arrays[3 + which], self._arrays[2], self.rank,
                                                     self.world, _lib.ptr(out), count, _lib.ptr(self._state),
                                                     _lib.stream_ptr(self.device))

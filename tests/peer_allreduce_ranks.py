@@ -42,6 +42,36 @@ def main():
         peer.allreduce(out)
         torch.cuda.synchronize()
         assert torch.equal(out, want), (rank, it, float((out.float() - want.float()).abs().max()))
+    # a prefill-sized message (the two-shot form under "auto" beyond 4 MiB on more than 2 ranks)
+    big = PeerAllReduce(2048 * 8192, algo=algo)
+    for it in range(3):
+        part = torch.randn(2048, 8192, device=dev, generator=gen).half()
+        want = reference(part)
+        big.partial(2048, 8192).copy_(part)
+        out = torch.empty(2048, 8192, dtype=torch.float16, device=dev)
+        big.allreduce(out)
+        torch.cuda.synchronize()
+        assert torch.equal(out, want), (rank, "big", it)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    nb = torch.randn(2048, 8192, device=dev, generator=gen).half()
+    dist.all_reduce(nb)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0.record()
+    for _ in range(10):
+        big.partial(2048, 8192)
+        big.allreduce(out)
+    e1.record()
+    torch.cuda.synchronize()
+    us_big_peer = e0.elapsed_time(e1) / 10 * 1e3
+    dist.barrier()
+    e0.record()
+    for _ in range(10):
+        dist.all_reduce(nb)
+    e1.record()
+    torch.cuda.synchronize()
+    us_big_nccl = e0.elapsed_time(e1) / 10 * 1e3
+    big.close()
     # replayed from a CUDA graph: the call counter lives on the device
     M, N = 64, 8192
     src = [torch.randn(M, N, device=dev, generator=gen).half() for _ in range(2)]
@@ -104,7 +134,8 @@ def main():
     two_shot = peer.two_shot
     peer.close()
     if rank == 0:
-        print(f"peer all-reduce ok: world={world} two_shot={two_shot} 1 MiB all-reduce {us_peer:.1f} us (peer kernel) vs {us_nccl:.1f} us (NCCL)", flush=True)
+        print(f"peer all-reduce ok: world={world} two_shot={two_shot} 1 MiB all-reduce {us_peer:.1f} us (peer kernel) vs {us_nccl:.1f} us (NCCL); "
+              f"32 MiB {us_big_peer:.0f} us vs {us_big_nccl:.0f} us", flush=True)
     dist.barrier()
     dist.destroy_process_group()
 
