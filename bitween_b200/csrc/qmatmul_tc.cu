@@ -824,9 +824,9 @@ int qmatmul_tc(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, cons
     CUtensorMap omap = wmap;
     const size_t oes = dtype_size(out_dtype);
     p.tma_store = 0;
-    // (only for tiles of 256 tokens: up to 128 tokens a thread stores at most 32 values, and the
-    // latency of the staged route outweighs them -- measured 8-14 % slower at 64 tokens)
-    if (p.bn == 256 && N >= TC_BM && (N * oes) % 16 == 0 && aligned_to(out, 16) && !p.ep.residual && p.ep.act != BW_ACT_SILU_MUL) {
+    // (token tiles of 64 and more: timed inside the kernel, the register-store epilogue of a 64-token tile
+    // took 3 us of a 25 us launch)
+    if (p.bn >= 64 && N >= TC_BM && (N * oes) % 16 == 0 && aligned_to(out, 16) && !p.ep.residual && p.ep.act != BW_ACT_SILU_MUL) {
         const cuuint64_t odims[2] = {(cuuint64_t)N, (cuuint64_t)M};
         const cuuint64_t ostrides[1] = {(cuuint64_t)N * oes};
         const cuuint32_t obox[2] = {(cuuint32_t)TC_BM, 32u};
