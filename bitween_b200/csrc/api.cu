@@ -55,6 +55,8 @@ int qmatmul_decode(const void *x, int x_dtype, int64_t M, int64_t N, int64_t K, 
                    int bits, int g, void *workspace, cudaStream_t st);
 int fake_quant(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int g, const float *scale, const float *zp,
                const void *value, int value_dtype, float *dq, float *wq, cudaStream_t st);
+int fake_quant_native(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int g, const void *scale, const void *zp,
+                      const void *value, void *dq, void *wq, cudaStream_t st);
 int fake_quant_backward(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int g, const float *scale, const float *zp,
                         const void *value, int value_dtype, const float *grad, float *gscale, float *gzp, cudaStream_t st);
 size_t peer_flag_bytes();
@@ -401,6 +403,21 @@ int bw_fake_quant(const void *w, int w_dtype, int64_t N, int64_t K, int bits, in
         !aligned_to(w_dq, 4) || !aligned_to(w_q, 4))
         return BW_ERR_ALIGN;
     return fake_quant(w, w_dtype, N, K, bits, group_size, scale, zero_point, value, value_dtype, w_dq, w_q, (cudaStream_t)stream);
+}
+
+int bw_fake_quant_native16(const void *w, int dtype, int64_t N, int64_t K, int bits, int group_size, const void *scale,
+                           const void *zero_point, const void *value, void *w_dq, void *w_q, void *stream) {
+    if (bits != 2 && bits != 4 && bits != 8) return BW_ERR_BITS;
+    if (group_size < 1) return BW_ERR_GROUP;
+    if (N < 0 || K < 0) return BW_ERR_SHAPE;
+    if (K % group_size != 0) return BW_ERR_GROUP;
+    if (dtype != BW_F16 && dtype != BW_BF16) return BW_ERR_DTYPE;
+    if (N * K == 0) return BW_OK;
+    if (!w || !scale || !zero_point || !w_dq) return BW_ERR_NULL;
+    if (!aligned_to(w, 2) || !aligned_to(scale, 2) || !aligned_to(zero_point, 2) || !aligned_to(value, 2) || !aligned_to(w_dq, 2) ||
+        !aligned_to(w_q, 2))
+        return BW_ERR_ALIGN;
+    return fake_quant_native(w, dtype, N, K, bits, group_size, scale, zero_point, value, w_dq, w_q, (cudaStream_t)stream);
 }
 
 int bw_fake_quant_backward(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int group_size, const float *scale,

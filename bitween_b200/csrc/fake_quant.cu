@@ -129,6 +129,27 @@ int launch(const void *w, int64_t N, int64_t K, int bits, int g, const float *sc
     return check_launch("fake_quant_kernel");
 }
 
+// The same pass when EVERYTHING is 16-bit (16-bit weights, min/max tuning off, so no fp32 tensor
+// promotes the arithmetic): the reference's torch ops then round every intermediate to the
+// weight's dtype -- w/scale, + zero_point, + value, the difference and the product -- which is
+// reproduced here by rounding after each fp32 operation (the fp32 result of one operation on two
+// 16-bit values, rounded to 16 bits, is the correctly rounded 16-bit result).  scale, zero_point,
+// value and both outputs have the weight's dtype.
+template <typename T> __device__ __forceinline__ float rnd16(float v) { return to_f32<T>(from_f32<T>(v)); }
+template <typename T>
+__global__ void __launch_bounds__(256)
+fake_quant_native_kernel(const T *__restrict__ w, int64_t total, int g, float qmax, const T *__restrict__ scale,
+                         const T *__restrict__ zp, const T *__restrict__ value, T *__restrict__ dq, T *__restrict__ wq) {
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+        const float s = to_f32<T>(scale[e / g]), z = to_f32<T>(zp[e / g]);
+        float t = rnd16<T>(__fadd_rn(rnd16<T>(__fdiv_rn(to_f32<T>(w[e]), s)), z));
+        if (value) t = rnd16<T>(__fadd_rn(t, to_f32<T>(value[e])));
+        const float q = clamp_keepnan(rintf(t), qmax);
+        dq[e] = from_f32<T>(__fmul_rn(s, rnd16<T>(__fsub_rn(q, z))));
+        if (wq) wq[e] = from_f32<T>(q);
+    }
+}
+
 // Backward of the pass above for the per-group parameters.  round() has zero gradient in the
 // reference's autograd graph, so w_dq = scale * (w_q - zero_point) gives
 //     d/d scale      = sum_group grad * (w_q - zero_point)
@@ -210,6 +231,26 @@ int launch_v(const void *w, int64_t N, int64_t K, int bits, int g, const float *
 }
 
 }  // namespace
+
+int fake_quant_native(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int g, const void *scale, const void *zp,
+                      const void *value, void *dq, void *wq, cudaStream_t st) {
+    const int64_t total = N * K;
+    if (total == 0) return BW_OK;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    const float qmax = (float)((1 << bits) - 1);
+    if (w_dtype == BW_F16)
+        fake_quant_native_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>((const __half *)w, total, g, qmax, (const __half *)scale,
+                                                                          (const __half *)zp, (const __half *)value, (__half *)dq, (__half *)wq);
+    else if (w_dtype == BW_BF16)
+        fake_quant_native_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>((const __nv_bfloat16 *)w, total, g, qmax,
+                                                                                 (const __nv_bfloat16 *)scale, (const __nv_bfloat16 *)zp,
+                                                                                 (const __nv_bfloat16 *)value, (__nv_bfloat16 *)dq,
+                                                                                 (__nv_bfloat16 *)wq);
+    else
+        return BW_ERR_DTYPE;
+    return check_launch("fake_quant_native_kernel");
+}
 
 int fake_quant(const void *w, int w_dtype, int64_t N, int64_t K, int bits, int g, const float *scale, const float *zp,
                const void *value, int value_dtype, float *dq, float *wq, cudaStream_t st) {

@@ -76,6 +76,8 @@ def _declare(L):
     L.bw_peer_allreduce2_f16.restype = i32
     L.bw_fake_quant.argtypes = [vp, i32, i64, i64, i32, i32, vp, vp, vp, i32, vp, vp, vp]
     L.bw_fake_quant.restype = i32
+    L.bw_fake_quant_native16.argtypes = [vp, i32, i64, i64, i32, i32, vp, vp, vp, vp, vp, vp]
+    L.bw_fake_quant_native16.restype = i32
     L.bw_fake_quant_backward.argtypes = [vp, i32, i64, i64, i32, i32, vp, vp, vp, i32, vp, vp, vp, vp]
     L.bw_fake_quant_backward.restype = i32
     L.bw_dequantize.argtypes = [vp, vp, i32, vp, i32, i64, i64, i32, i32, vp, i32, vp]

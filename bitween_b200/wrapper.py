@@ -18,7 +18,7 @@ What runs where on every training step (bitween/wrapper.py:116-172):
 The fused kernels compute in fp32, which is what the reference computes whenever an fp32
 parameter takes part (fp32 weights, or min/max tuning on: `torch.ones` factors are fp32 and
 promote everything).  With 16-bit weights AND min/max tuning off the reference rounds every
-intermediate to 16 bits; that case runs the reference's sequence of torch ops on the GPU instead.
+intermediate to 16 bits; `bw_fake_quant_native16` does the same, rounding after each operation.
 """
 from typing import List
 
@@ -185,16 +185,23 @@ class WrapperLinear(nn.Module):
         return w_dq, w_q.view(N, G, self.group_size), scale, zero_point
 
     def _all_16bit_path(self, scale, zero_point):
-        # 16-bit weights with min/max tuning off: every intermediate is rounded to the weight's
-        # dtype in the reference, which the fp32 kernel does not do; same torch ops here.
+        # 16-bit weights with min/max tuning off: every intermediate is rounded to the weight's dtype in
+        # the reference (no fp32 tensor takes part); bw_fake_quant_native16 rounds after every operation.
         N, K = self.orig_weight.shape
-        grouped = self.orig_weight.view(N, K // self.group_size, self.group_size)
-        s3, z3 = scale.unsqueeze(-1), zero_point.unsqueeze(-1)
-        t = grouped / s3 + z3
-        if self.value is not None:
-            t = t + self.value.view_as(grouped)
-        w_q = torch.clamp(torch.round(t), 0, (1 << self.bits) - 1)
-        return (s3 * (w_q - z3)).view(N, K), w_q, scale, zero_point
+        w = self.orig_weight
+        _lib.require_cuda(w, "orig_weight")
+        scale, zero_point = scale.contiguous(), zero_point.contiguous()
+        v = None if self.value is None else self.value.detach().contiguous()
+        dq = torch.empty_like(w)
+        wq = torch.empty_like(w)
+        with torch.cuda.device(w.device):
+            rc = _lib.lib().bw_fake_quant_native16(_lib.ptr(w), _lib.dtype_code(w.dtype), N, K, self.bits, self.group_size,
+                                                   _lib.ptr(scale), _lib.ptr(zero_point), None if v is None else _lib.ptr(v),
+                                                   _lib.ptr(dq), _lib.ptr(wq), _lib.stream_ptr(w.device))
+        _lib.check(rc)
+        # (nothing here has a gradient in the reference either: round() cuts `value` off, and there are no
+        # min/max factors in this mode)
+        return dq, wq.view(N, K // self.group_size, self.group_size), scale, zero_point
 
     def forward(self, x):
         scale, zero_point = self._group_params()

@@ -283,6 +283,16 @@ BW_API int bw_fake_quant(const void *w, int w_dtype, int64_t N, int64_t K, int b
                   float *w_dq, float *w_q, void *stream);
 
 /*
+ * bw_fake_quant when every tensor is 16-bit (16-bit weights and min/max tuning off: nothing promotes
+ * the reference's arithmetic to fp32, bitween/wrapper.py:143-155 then rounds each intermediate to the
+ * weight's dtype): w, scale, zero_point, value (or NULL), w_dq and w_q (or NULL) all have `dtype`
+ * (BW_F16 | BW_BF16); every operation is rounded to it, bit-identical to the torch ops.
+ */
+BW_API int bw_fake_quant_native16(const void *w, int dtype, int64_t N, int64_t K, int bits, int group_size,
+                           const void *scale, const void *zero_point, const void *value, void *w_dq,
+                           void *w_q, void *stream);
+
+/*
  * Backward of bw_fake_quant for the per-group parameters, as the reference's autograd graph
  * gives it (round() passes no gradient, bitween/wrapper.py:152-155):
  *     grad_scale      = sum over the group of grad_w_dq * (w_q - zero_point)

@@ -228,3 +228,32 @@ def wrapper_param_grads(w32, scale, zp, value32, grad, bits, group_size):
     q3 = q.astype(np.float64).reshape(g3.shape)
     z = np.asarray(zp, dtype=np.float64)
     return (g3 * (q3 - z[:, :, None])).sum(-1), -np.asarray(scale, dtype=np.float64) * g3.sum(-1)
+
+
+def _round_to(a, dtype):
+    """fp32 values rounded to the 16-bit format `dtype` (and back to fp32)."""
+    return bits_to_f32(f16_bits(a) if dtype == F16 else bf16_bits(a), dtype).reshape(np.shape(a))
+
+
+def wrapper_fake_quant_native(w_bits, value_bits, dtype, bits, group_size):
+    """bitween/wrapper.py:127-155 when every tensor has the 16-bit `dtype` (16-bit weights, min/max
+    tuning off): each operation is an fp32 operation on 16-bit values rounded back to 16 bits, which is
+    how torch evaluates it.  Inputs are uint16 bit patterns [N,K]; returns (w_dq, w_q [N,K], scale,
+    zero_point [N,G]) as fp32 arrays holding 16-bit-representable values."""
+    w = bits_to_f32(np.asarray(w_bits), dtype)
+    N, K = w.shape
+    g3 = w.reshape(N, K // group_size, group_size)
+    rd = lambda a: _round_to(a, dtype)   # noqa: E731
+    with np.errstate(all="ignore"):
+        w_min, w_max = g3.min(-1, keepdims=True), g3.max(-1, keepdims=True)
+        scale = rd(rd(w_max - w_min) / np.float32((1 << bits) - 1))
+        floor = rd(np.float32(1e-8))                       # 1e-8 in the 16-bit format (0 in fp16)
+        scale = np.where(scale < floor, floor, scale).astype(np.float32)
+        zp = rd(-w_min / scale)
+        t = rd(rd(g3 / scale) + zp)
+        if value_bits is not None:
+            t = rd(t + bits_to_f32(np.asarray(value_bits), dtype).reshape(g3.shape))
+        r = np.rint(t)
+        q = np.where(np.isnan(r), r, np.minimum(np.maximum(r, np.float32(0)), np.float32((1 << bits) - 1))).astype(np.float32)
+        dq = rd(scale * rd(q - zp))
+    return dq.reshape(N, K), q.reshape(N, K), scale[:, :, 0], zp[:, :, 0]

@@ -43,7 +43,10 @@ def main(ref_root):
               (8, 64, "f32", False, True, "rand"), (4, 64, "f32", False, False, "rand"),
               (4, 32, "f32", True, True, "constant"), (4, 32, "f16", True, True, "constant"),
               (4, 32, "f32", True, True, "ties"), (2, 32, "f32", True, True, "collapsed"),
-              (8, 32, "f32", True, True, "big_value")]
+              (8, 32, "f32", True, True, "big_value"),
+              # every tensor 16-bit (min/max tuning off): each intermediate is rounded to the weight's dtype
+              (4, 128, "f16", False, True, "rand"), (8, 32, "bf16", False, True, "rand"), (2, 64, "f16", False, False, "rand"),
+              (4, 64, "bf16", False, False, "rand"), (8, 128, "f16", False, True, "big_value")]
     for bits, g, dt, minmax, rnd, kind in specs:
         N = 6
         K = 2 * g if g >= 64 else 4 * g

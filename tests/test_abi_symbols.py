@@ -62,3 +62,5 @@ def test_status_strings_and_argument_validation_need_no_gpu():
     # the gated epilogue: the activation code is checked, and N must hold whole (gate, up) row pairs in fours
     assert L.bw_qmatmul_fused(z, 1, 4, 6, 64, z, z, z, z, z, 1, 4, 32, _lib.Epilogue(_lib.ACT_SILU_MUL, None), z, 0, z) == 3   # BW_ERR_SHAPE
     assert L.bw_qmatmul_fused(z, 1, 4, 8, 64, z, z, z, z, z, 1, 4, 32, _lib.Epilogue(7, None), z, 0, z) == 9                   # unknown activation
+    assert L.bw_fake_quant_native16(z, 0, 4, 64, 4, 32, z, z, z, z, z, z) == 4        # fp32 is not a 16-bit dtype
+    assert L.bw_fake_quant_native16(z, 1, 4, 64, 4, 32, z, z, z, z, z, z) == 6

@@ -47,9 +47,19 @@ def case_inputs(gold, c):
 
 def test_fake_quant_matches_reference_bit_exact(cases, gold):
     assert len(cases) >= 40
+    native = 0
     for c in cases:
-        assert c["out_dtype"] == "float32"
         n = c["name"]
+        if c["out_dtype"] != "float32":
+            # every tensor 16-bit: the per-operation rounding of the reference
+            assert not c["minmax"] and c["out_dtype"] == {"f16": "float16", "bf16": "bfloat16"}[c["dtype"]]
+            dt = DT[c["dtype"]]
+            dq, q, scale, zp = oracle.wrapper_fake_quant_native(gold[n + "/w"], gold[n + "/value"] if c["round"] else None,
+                                                                dt, c["bits"], c["g"])
+            for got, key in ((scale, "/scale"), (zp, "/zp"), (q, "/w_q"), (dq, "/w_dq")):
+                assert same_numbers(got, oracle.bits_to_f32(gold[n + key], dt).reshape(got.shape)), (n, key)
+            native += 1
+            continue
         w, mn, mx, v = case_inputs(gold, c)
         scale, zp = oracle.wrapper_group_params(w, c["bits"], c["g"], mn, mx)
         assert np.array_equal(scale.view(np.uint32), gold[n + "/scale"].view(np.uint32)), n
@@ -57,6 +67,7 @@ def test_fake_quant_matches_reference_bit_exact(cases, gold):
         dq, q = oracle.wrapper_fake_quant(w, scale, zp, v, c["bits"], c["g"])
         assert same_numbers(q, gold[n + "/w_q"]), n
         assert same_numbers(dq, gold[n + "/w_dq"]), n
+    assert native >= 5
 
 
 def test_param_grads_match_reference_autograd(cases, gold):
