@@ -5,7 +5,8 @@
  *
  * Conventions for every entry point:
  *   - plain pointers and sizes only; every pointer is DEVICE memory owned by the caller
- *     unless the name says host; nothing the caller sees is allocated here
+ *     unless the name says host; nothing the caller sees is allocated here (the one exception
+ *     is bw_peer_alloc / bw_peer_free: memory that other processes map needs its own allocation)
  *   - asynchronous on `stream` (a cudaStream_t passed as void*; NULL = default stream),
  *     on the CUDA device that is current in the calling thread
  *   - returns a bw_status (0 = BW_OK); never throws, aborts or traps
